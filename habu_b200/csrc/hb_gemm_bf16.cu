@@ -1,0 +1,400 @@
+// bf16 GEMM for sm_100a: C[M,N] = epilogue(A[M,K] . B[K,N]), fp32 accumulation in tensor
+// memory, bf16 output.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of A (128 x 64) and B (BN x 64)
+//               tiles, 128-byte swizzled, into a STAGES-deep shared-memory ring;
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) four
+//               times per 64-wide k-block, tcgen05.commit releases the ring slot, and a
+//               final commit per tile publishes the accumulator;
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per
+//               thread), apply the epilogue, round to bf16 once, 16-byte global stores.
+// Two accumulators (2 x BN TMEM columns) let the epilogue of tile i overlap the mainloop
+// of tile i+1.  Operands may be K-major (K contiguous) or MN-major; both are described to
+// the tensor core by shared-memory descriptors over the layout TMA writes.
+//
+// Algorithmic traffic per launch: (M*K + N*K + M*N) * 2 bytes; work 2*M*N*K flop.
+#include "hb_internal.h"
+#include "hb_ptx.cuh"
+
+namespace {
+
+using namespace hb;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  __nv_bfloat16* C;
+  const __nv_bfloat16* R;   // residual (or null)
+  int M, N, K;
+  int64_t ldc, ldr;
+  int tiles_m, tiles_n;
+  int raster_group;         // tiles_m grouped per sweep over N (L2 reuse)
+  int epilogue;
+  int a_mn, b_mn;           // operand is MN-major
+  int32_t* status;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_BAR = OFF_B + STAGES * B_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int OFF_TMEM_PTR = OFF_BAR + NUM_BARS * 8;
+  static constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
+  static constexpr int TOTAL = OFF_ABORT + 4;
+  static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& tm, int& tn) {
+  // Sweep N inside groups of `raster_group` M-tiles so that concurrently resident CTAs
+  // share A rows and B columns in L2.
+  const int g = p.raster_group;
+  const int per_group = g * p.tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * g;
+  const int rows = min(g, p.tiles_m - first_m);
+  const int in_group = tile - group * per_group;
+  tm = first_m + in_group % rows;
+  tn = in_group / rows;
+}
+
+__device__ __forceinline__ float gelu_erf(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const uint32_t sA = smem_base + L::OFF_A;
+  const uint32_t sB = smem_base + L::OFF_B;
+  const uint32_t bar_full = smem_base + L::OFF_BAR;
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;
+  const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_TMEM_PTR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::OFF_ABORT);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
+                                 : (2 * BN <= 256) ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + a * 8, 1);
+      mbar_init(bar_tempty + a * 8, 128);
+    }
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), TMEM_COLS);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, p, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + s * 8, phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar_full + s * 8, L::A_BYTES + L::B_BYTES);
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_2d(sA + s * L::A_BYTES, &tmA, bar_full + s * 8, k0, m0);
+          } else {
+            // M-major A: two boxes of 64 (M) x 64 (K); box c holds rows m0+64c..+63
+            tma_load_2d(sA + s * L::A_BYTES, &tmA, bar_full + s * 8, m0, k0);
+            tma_load_2d(sA + s * L::A_BYTES + L::A_BYTES / 2, &tmA, bar_full + s * 8, m0 + 64, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sB + s * L::B_BYTES, &tmB, bar_full + s * 8, k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + s * L::B_BYTES + c * (64 * BK * 2), &tmB, bar_full + s * 8,
+                          n0 + 64 * c, k0);
+          }
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+      if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 1; }
+      // Drain: every armed load has landed once the consumer side has released (or the
+      // barrier phase completed); wait for the slots still in flight, bounded.
+      // (In the normal path the MMA warp consumed them already.)
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = umma_idesc_bf16(BM, BN, p.a_mn, p.b_mn);
+      int s = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + s * 8, phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = sA + s * L::A_BYTES;
+          const uint32_t b_addr = sB + s * L::B_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 16 bf16 = 32 bytes further along the 128-byte swizzled row.
+            // MN-major: 16 k-rows = two 8-row groups of 1024 bytes further.
+            const uint64_t ad = p.a_mn ? umma_desc_mn_sw128(a_addr + k * 2048, L::A_BYTES / 2, 1024)
+                                       : umma_desc_k_sw128(a_addr + k * 32);
+            const uint64_t bd = p.b_mn ? umma_desc_mn_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
+                                       : umma_desc_k_sw128(b_addr + k * 32);
+            umma_ss<1>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit<1>(bar_empty + s * 8);
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit<1>(bar_tfull + acc * 8);
+      }
+      if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 2; }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;               // TMEM lane quarter this warp may access
+    const int row_in_tile = q * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      int tm, tn;
+      tile_coords(tile, p, tm, tn);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(bar_tfull + acc * 8, acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + row_in_tile;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
+        tmem_wait_ld();
+        const int col0 = tn * BN + c * 32;
+        if (row < p.M && col0 < p.N) {
+          if (p.epilogue == HB_EPI_SWIGLU) {
+            // columns interleave (gate, up): out[j] = silu(acc[2j]) * acc[2j+1]
+            const int ocol0 = col0 >> 1;
+            const int on = p.N >> 1;
+            __nv_bfloat16* dst = p.C + static_cast<int64_t>(row) * p.ldc + ocol0;
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float g0 = __uint_as_float(v[4 * j]), u0 = __uint_as_float(v[4 * j + 1]);
+              const float g1 = __uint_as_float(v[4 * j + 2]), u1 = __uint_as_float(v[4 * j + 3]);
+              o[j] = pack_bf16x2(silu(g0) * u0, silu(g1) * u1);
+            }
+            if (vec_ok && ocol0 + 16 <= on) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+              d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            } else {
+              const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(o);
+              for (int j = 0; j < 16; ++j)
+                if (ocol0 + j < on) dst[j] = ob[j];
+            }
+          } else {
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+            if (p.epilogue == HB_EPI_GELU) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+            } else if (p.epilogue == HB_EPI_RESIDUAL) {
+              const __nv_bfloat16* r = p.R + static_cast<int64_t>(row) * p.ldr + col0;
+              if (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0) &&
+                  col0 + 32 <= p.N) {
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {
+                  const uint4 rv = __ldg(reinterpret_cast<const uint4*>(r) + j4);
+                  const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 rf = __bfloat1622float2(r2[j]);
+                    f[j4 * 8 + 2 * j] += rf.x;
+                    f[j4 * 8 + 2 * j + 1] += rf.y;
+                  }
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) f[j] += __bfloat162float(r[j]);
+              }
+            }
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+            __nv_bfloat16* dst = p.C + static_cast<int64_t>(row) * p.ldc + col0;
+            if (vec_ok && col0 + 32 <= p.N) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                d4[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+            } else {
+              const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(o);
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = ob[j];
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_tempty + acc * 8);
+    }
+    if (!ok && p.status && lane == 0) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 3; }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, TMEM_COLS);
+  }
+}
+
+struct GemmConfig {
+  int bn, stages;
+  int raster_group;
+};
+// config_id -> (tile N, stages, raster group).  Tile M is 128, tile K 64, cluster 1.
+constexpr GemmConfig kConfigs[] = {
+    {256, 4, 8},  {256, 4, 16}, {256, 4, 4},  {256, 4, 2},
+    {128, 6, 8},  {128, 6, 16}, {128, 6, 4},
+    {64, 8, 8},   {64, 8, 16},
+};
+constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
+
+template <int BN, int STAGES>
+hb_status launch_cfg(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = hb_gemm_bf16_kernel<BN, STAGES>;
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx->device & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         L::DYN_BYTES);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(gemm)");
+    attr_set[ctx->device & 63] = true;
+  }
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  kern<<<grid, GEMM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, p);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "gemm launch");
+}
+
+}  // namespace
+
+int hb_gemm_num_configs() { return kNumConfigs; }
+
+void hb_gemm_config_describe(int id, hb_tune_result* out) {
+  const GemmConfig& c = kConfigs[id];
+  out->config_id = id;
+  out->tile_m = BM;
+  out->tile_n = c.bn;
+  out->tile_k = BK;
+  out->stages = c.stages;
+  out->cluster = 1;
+  out->raster_group = c.raster_group;
+  out->split_k = 1;
+}
+
+hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id) {
+  if (config_id < 0 || config_id >= kNumConfigs)
+    return hb_fail(ctx, HB_ERR_INVALID, "matmul: config_id %d out of range [0,%d)", config_id,
+                   kNumConfigs);
+  const GemmConfig cfg = kConfigs[config_id];
+  CUtensorMap tmA, tmB;
+  hb_status st;
+  // A: K-major -> dims (K, M), box (64, 128); M-major -> dims (M, K), box (64, 64) x2.
+  if (!a.a_mn_major) {
+    uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.M};
+    uint64_t strides[1] = {(uint64_t)a.lda * 2};
+    uint32_t box[2] = {BK, BM};
+    st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    uint64_t dims[2] = {(uint64_t)a.M, (uint64_t)a.K};
+    uint64_t strides[1] = {(uint64_t)a.lda * 2};
+    uint32_t box[2] = {64, BK};
+    st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (st != HB_OK) return st;
+  if (!a.b_mn_major) {
+    uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.N};
+    uint64_t strides[1] = {(uint64_t)a.ldb * 2};
+    uint32_t box[2] = {BK, (uint32_t)cfg.bn};
+    st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  } else {
+    uint64_t dims[2] = {(uint64_t)a.N, (uint64_t)a.K};
+    uint64_t strides[1] = {(uint64_t)a.ldb * 2};
+    uint32_t box[2] = {64, BK};
+    st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  if (st != HB_OK) return st;
+
+  GemmParams p;
+  p.C = static_cast<__nv_bfloat16*>(a.C);
+  p.R = static_cast<const __nv_bfloat16*>(a.residual);
+  p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
+  p.ldc = a.ldc; p.ldr = a.ldr;
+  p.raster_group = cfg.raster_group;
+  p.epilogue = a.epilogue;
+  p.a_mn = a.a_mn_major; p.b_mn = a.b_mn_major;
+  p.status = ctx->d_status;
+  switch (cfg.bn) {
+    case 256: return launch_cfg<256, 4>(ctx, tmA, tmB, p);
+    case 128: return launch_cfg<128, 6>(ctx, tmA, tmB, p);
+    case 64:  return launch_cfg<64, 8>(ctx, tmA, tmB, p);
+  }
+  return hb_fail(ctx, HB_ERR_INVALID, "matmul: bad config");
+}

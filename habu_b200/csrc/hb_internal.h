@@ -1,0 +1,82 @@
+// Internal (non-ABI) declarations shared by the translation units of libhabu_b200.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/habu_b200.h"
+
+// Device status word layout (int32[4]): [0] first error code, [1] kernel tag that
+// reported it, [2] detail (e.g. which wait), [3] reserved.
+enum { HB_KTAG_GEMM = 1, HB_KTAG_ATTN = 2, HB_KTAG_ALLREDUCE = 3, HB_KTAG_SPLITK = 4 };
+
+// Scratch slots: kernel workspace (split-K partials), host-call staging, autotune operands.
+enum { HB_SCRATCH_WORKSPACE = 0, HB_SCRATCH_STAGING = 1, HB_SCRATCH_TUNE = 2, HB_NUM_SCRATCH = 3 };
+
+struct hb_tune_entry {
+  int32_t config_id;
+  float ms;
+};
+
+struct hb_p2p_state {
+  int world = 0, rank = 0;
+  size_t bytes = 0;
+  void* local = nullptr;              // this rank's symmetric buffer (data + flags)
+  std::vector<void*> peers;           // mapped base pointers, peers[rank] == local
+  void** d_peers = nullptr;           // device copy of `peers`
+  uint32_t epoch = 0;
+};
+
+struct hb_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;      // stream in use
+  cudaStream_t own_stream = nullptr;  // created by the context
+  int32_t* d_status = nullptr;
+  int32_t* h_status = nullptr;        // pinned
+  int64_t launches = 0;
+  std::string err;
+  std::map<std::string, hb_tune_entry> tune_cache;
+  // collectives
+  void* nccl_comm = nullptr;
+  int world = 1, rank = 0;
+  hb_p2p_state p2p;
+  // grow-only device buffers owned by the context
+  void* scratch[HB_NUM_SCRATCH] = {};
+  size_t scratch_bytes[HB_NUM_SCRATCH] = {};
+  std::vector<void*> allocations;
+};
+
+hb_status hb_fail(hb_ctx* ctx, hb_status code, const char* fmt, ...);
+hb_status hb_check_cuda(hb_ctx* ctx, cudaError_t e, const char* what);
+// Grow-only scratch buffer `slot` on the context's device.
+hb_status hb_get_scratch(hb_ctx* ctx, int slot, size_t bytes, void** out);
+
+// cuTensorMapEncodeTiled fetched through the runtime (no link against libcuda).
+// dims/strides innermost first; strides in bytes for dims 1..rank-1.
+hb_status hb_make_tensor_map(hb_ctx* ctx, CUtensorMap* out, CUtensorMapDataType dt, int rank,
+                             const void* base, const uint64_t* dims, const uint64_t* strides_bytes,
+                             const uint32_t* box, CUtensorMapSwizzle swizzle);
+
+std::string hb_tune_key(const hb_op_desc& d, int sm_count, int world);
+
+// Kernel launchers (each validates nothing: callers validated already).
+struct hb_gemm_args {
+  const void* A;
+  const void* B;
+  void* C;
+  int64_t M, N, K;
+  int64_t lda, ldb, ldc;   // elements
+  int a_mn_major, b_mn_major;
+  int epilogue;
+  const void* residual;
+  int64_t ldr;
+};
+hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id);
+hb_status hb_launch_gemm_f32(hb_ctx* ctx, const hb_gemm_args& a);
+int hb_gemm_pick_config(hb_ctx* ctx, const hb_gemm_args& a);

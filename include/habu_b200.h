@@ -1,0 +1,188 @@
+/*
+ * habu_b200.h -- C ABI of libhabu_b200.so, the sm_100a kernel library behind the
+ * model-IR executor's dense hot path (matmul / attention / collective nodes and the
+ * autotune entry point).
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an
+ * `hb_status`, and never throws, aborts or traps.  All operators are asynchronous on
+ * the context's stream; `hb_sync` is the only blocking call, so a foreign runtime
+ * (e.g. OCaml `foreign_stubs`) can release its runtime lock there and nowhere else.
+ *
+ * Reference interface: the reference project (joelreymont/habu) has NO operator, plugin
+ * or FFI surface for this path -- `src/lib/dune:1-12` holds only `library`, `ocamllex`
+ * and `menhir` stanzas, with no `foreign_stubs` and no `external` declarations anywhere.
+ * The conventions the reference does pin are mirrored where they apply:
+ *   - errors are values, never exceptions: `` `Invalid | `Duplicate | `Not_found ``
+ *     of `src/lib/error.ml:18-26` map to HB_ERR_INVALID / HB_ERR_DUPLICATE /
+ *     HB_ERR_NOT_FOUND;
+ *   - constructors validate and return a result (`Space.make`, `src/lib/sleigh.ml:50-62`):
+ *     every operator validates its descriptors on the host before any launch;
+ *   - a list of variant-tagged definitions is walked in order and dispatched on its tag
+ *     (`lift_defs_exn`, `tree.ml:786-811`): `hb_graph_*` keeps the same shape.
+ */
+#ifndef HABU_B200_H
+#define HABU_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t hb_status;
+enum {
+  HB_OK = 0,
+  HB_ERR_INVALID = 1,     /* `Invalid   (src/lib/error.ml:19) */
+  HB_ERR_NOT_FOUND = 2,   /* `Not_found (src/lib/error.ml:21) */
+  HB_ERR_DUPLICATE = 3,   /* `Duplicate (src/lib/error.ml:20) */
+  HB_ERR_CUDA = 4,
+  HB_ERR_NCCL = 5,
+  HB_ERR_TIMEOUT = 6,     /* a bounded device-side wait gave up */
+  HB_ERR_UNSUPPORTED = 7,
+  HB_ERR_NOMEM = 8
+};
+
+enum { HB_F32 = 0, HB_BF16 = 1, HB_I32 = 2 };
+
+/* POD tensor view: `ptr` is a DEVICE pointer, strides are in ELEMENTS. */
+typedef struct hb_tensor {
+  void* ptr;
+  int32_t dtype;
+  int32_t rank;
+  int64_t shape[4];
+  int64_t stride[4];
+} hb_tensor;
+
+typedef struct hb_ctx hb_ctx;
+
+/* ---- context / memory (no reference counterpart: the reference never leaves the host) */
+hb_status hb_ctx_create(int32_t device, hb_ctx** out);
+hb_status hb_ctx_destroy(hb_ctx* ctx);
+/* Use a caller-owned CUDA stream (a cudaStream_t passed as void*); NULL restores the
+ * context's own stream. */
+hb_status hb_ctx_set_stream(hb_ctx* ctx, void* cuda_stream);
+const char* hb_last_error_string(hb_ctx* ctx);
+hb_status hb_alloc(hb_ctx* ctx, size_t bytes, void** dev_ptr);
+hb_status hb_free(hb_ctx* ctx, void* dev_ptr);
+hb_status hb_upload(hb_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+hb_status hb_download(hb_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+/* Blocks until the stream drains; returns HB_ERR_TIMEOUT if any kernel's bounded wait
+ * gave up since the last call, HB_ERR_CUDA on an asynchronous CUDA error. */
+hb_status hb_sync(hb_ctx* ctx);
+/* Number of this library's kernels launched through `ctx` since creation. */
+int64_t hb_launch_count(hb_ctx* ctx);
+int32_t hb_sm_count(hb_ctx* ctx);
+
+/* ---- model-IR matmul node ---------------------------------------------------------
+ * C[M,N] = epilogue(A[M,K] . B[K,N]).  bf16 operands, fp32 accumulation in tensor
+ * memory, bf16 output (HB_BF16), or fp32 throughout on CUDA cores (HB_F32).
+ * Operand layouts are taken from the strides: A is K-contiguous (row-major) or
+ * M-contiguous; B is K-contiguous ("column-major B", stride[0] == 1) or N-contiguous.
+ * C is row-major.  Replaces: nothing -- the reference has no matmul; `MUL`/`FMUL`
+ * (`src/lib/sleigh.ml:219,224`) are syntax constructors that are never evaluated. */
+enum {
+  HB_EPI_NONE = 0,
+  HB_EPI_GELU = 1,          /* erf-exact GELU */
+  HB_EPI_SWIGLU = 2,        /* B's N columns interleave (gate,up); C has N/2 columns */
+  HB_EPI_RESIDUAL = 3       /* C = A.B + R, R row-major bf16 shaped like C */
+};
+typedef struct hb_matmul_opts {
+  int32_t epilogue;         /* HB_EPI_* */
+  int32_t config_id;        /* -1: use the autotune cache / heuristic */
+  const void* residual;     /* device pointer, HB_EPI_RESIDUAL only */
+  int64_t residual_ld;      /* elements */
+} hb_matmul_opts;
+hb_status hb_matmul(hb_ctx* ctx, const hb_tensor* A, const hb_tensor* B, hb_tensor* C,
+                    const hb_matmul_opts* opts);
+/* Same node with HOST buffers: uploads A and B, runs, downloads C, synchronises.
+ * A is [M,K] row-major, B is column-major (K contiguous per column), C row-major. */
+hb_status hb_matmul_host(hb_ctx* ctx, const void* A_host, const void* B_host, void* C_host,
+                         int64_t M, int64_t N, int64_t K, int32_t dtype);
+
+/* ---- model-IR attention node --------------------------------------------------------
+ * O = softmax(scale * Q K^T + causal mask) V per (batch, head).  Tensors are
+ * [batch, seq, heads, head_dim] bf16 (token-major); n_q_heads must be a multiple of
+ * n_kv_heads (grouped-query attention).  fp32 scores, fp32 running max/sum, P rounded
+ * to bf16 before the PV product.  `lse` (optional, fp32 [batch, heads, seq]) receives
+ * log-sum-exp of the scaled scores.  No reference counterpart. */
+typedef struct hb_attn_opts {
+  int32_t causal;
+  float scale;
+  void* lse;
+  int32_t config_id;
+} hb_attn_opts;
+hb_status hb_attention(hb_ctx* ctx, const hb_tensor* Q, const hb_tensor* K,
+                       const hb_tensor* V, hb_tensor* O, const hb_attn_opts* opts);
+hb_status hb_attention_host(hb_ctx* ctx, const void* Q, const void* K, const void* V, void* O,
+                            int64_t batch, int64_t seq, int64_t n_q_heads,
+                            int64_t n_kv_heads, int64_t head_dim, int32_t causal,
+                            float scale);
+
+/* ---- glue operators the decoder / MLP configurations put on the path ------------- */
+/* y = x * rsqrt(mean(x^2) + eps) * gain; rows x cols bf16, gain bf16[cols]. If
+ * `residual_inout` is non-NULL it is first updated in place: residual += x, and the
+ * norm is taken of the updated residual (fused residual add). */
+hb_status hb_rmsnorm(hb_ctx* ctx, const void* x, const void* gain, void* y,
+                     void* residual_inout, int64_t rows, int64_t cols, float eps);
+/* Rotate-half RoPE in place over x[tokens, heads, head_dim]; position of token t is
+ * pos0 + (t % seq). theta_i = base^(-2i/head_dim). */
+hb_status hb_rope(hb_ctx* ctx, void* x, int64_t tokens, int64_t seq, int64_t heads,
+                  int64_t head_dim, int64_t row_stride, float base, int64_t pos0);
+/* out[t, :] = table[ids[t], :] (bit-exact gather). */
+hb_status hb_embedding(hb_ctx* ctx, const void* table, const int32_t* ids, void* out,
+                       int64_t tokens, int64_t vocab, int64_t dim);
+/* out[r, j] = silu(x[r, j]) * x[r, half + j]  for x[rows, 2*half] bf16. */
+hb_status hb_swiglu(hb_ctx* ctx, const void* x, void* out, int64_t rows, int64_t half);
+hb_status hb_gelu(hb_ctx* ctx, const void* x, void* y, int64_t n);
+hb_status hb_add(hb_ctx* ctx, const void* a, const void* b, void* out, int64_t n);
+/* argmax over the last dimension, first index wins ties (bit-exact). */
+hb_status hb_argmax(hb_ctx* ctx, const void* x, int32_t* out, int64_t rows, int64_t cols);
+
+/* ---- model-IR collective node ----------------------------------------------------
+ * Sum-allreduce of `count` bf16/f32 elements in place across the ranks of the
+ * communicator bound to `ctx`.  HB_AR_NCCL enqueues ncclAllReduce on the stream;
+ * HB_AR_P2P runs this library's two-shot kernel over peer-mapped buffers (plain peer
+ * loads and stores, bounded flag waits). No reference counterpart. */
+enum { HB_AR_AUTO = 0, HB_AR_NCCL = 1, HB_AR_P2P = 2 };
+#define HB_UNIQUE_ID_BYTES 128
+#define HB_IPC_HANDLE_BYTES 64
+hb_status hb_comm_unique_id(void* id_out /* HB_UNIQUE_ID_BYTES */);
+hb_status hb_comm_init_rank(hb_ctx* ctx, int32_t world, int32_t rank, const void* unique_id);
+hb_status hb_comm_destroy(hb_ctx* ctx);
+/* P2P set-up: each rank allocates a symmetric buffer, exports its handle, exchanges
+ * handles out of band (any host channel) and opens its peers'. */
+hb_status hb_p2p_alloc(hb_ctx* ctx, size_t bytes, void** dev_ptr, void* handle_out);
+hb_status hb_p2p_attach(hb_ctx* ctx, int32_t world, int32_t rank, const void* all_handles,
+                        size_t bytes);
+hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo);
+
+/* ---- autotune entry point ----------------------------------------------------------
+ * Searches tile shape / cluster shape / stage count / raster order for one problem
+ * shape by timing each candidate on the device, records the winner in the context's
+ * cache, and can persist the cache as text.  No reference counterpart. */
+enum { HB_OP_MATMUL = 0, HB_OP_ATTENTION = 1 };
+enum { HB_TUNE_CACHED = 0, HB_TUNE_SEARCH = 1 };
+typedef struct hb_op_desc {
+  int32_t op;              /* HB_OP_* */
+  int32_t dtype;
+  int64_t m, n, k;         /* matmul: M,N,K; attention: batch*heads, seq, head_dim */
+  int32_t layout;          /* matmul: bit0 A is M-major, bit1 B is N-major */
+  int32_t epilogue;
+} hb_op_desc;
+typedef struct hb_tune_result {
+  int32_t config_id;
+  int32_t tile_m, tile_n, tile_k, stages, cluster, raster_group, split_k;
+  float ms;
+  float tflops;
+} hb_tune_result;
+hb_status hb_autotune(hb_ctx* ctx, const hb_op_desc* desc, int32_t mode, hb_tune_result* out);
+hb_status hb_tune_cache_load(hb_ctx* ctx, const char* path);
+hb_status hb_tune_cache_save(hb_ctx* ctx, const char* path);
+int32_t hb_matmul_config_count(void);
+hb_status hb_matmul_config_info(int32_t config_id, hb_tune_result* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HABU_B200_H */
