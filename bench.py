@@ -1,0 +1,310 @@
+#!/usr/bin/env python
+"""Benchmark of the dense hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|skinny|attention]
+                    [--impl ours|reference]
+
+One "step" is one pass of the hot path over one batch of seeded synthetic input.  The
+default workload is the bf16 GEMM at M=N=K=8192 (A row-major, B column-major, fp32
+accumulate, bf16 output).  Rank 0 prints ONE JSON line:
+
+  value         whole-job TFLOP/s with operands resident in HBM, CUDA-event timed on the
+                launching stream, max over ranks (N>1: independent replicas, one per GPU);
+  e2e           the same metric through the host-buffer C-ABI call (pinned host buffers,
+                host->device and device->host copies inside the timed region);
+  roofline      dominant kernel: algorithmic flop per launch / measured launch duration,
+                against the measured cuBLAS bf16 peak in MEASURED_PEAKS.json;
+  cpu_baseline  the CPU oracle timed on the host cores on a bounded sample (rank 0, N=1).
+
+``--impl reference`` times the reference arm: the reference project has no implementation
+of this path, so the CPU oracle (a port, all host threads) stands in for it.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+SEED = 0x48414255
+NVSMI_Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+           "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+           "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
+# (profiles/), scaled to the full launch; None where not captured.
+NCU_TRAFFIC_BYTES = {"gemm": 1.404330e9 + 129.282304e6, "skinny": None, "attention": None}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"bf16_burst": d["bf16_tflops"], "bf16_sustained": d["bf16_tflops_sustained"],
+                "hbm": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_burst": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU during the timed region."""
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={NVSMI_Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v == "Active"})
+        pw = [float(r[3]) for r in self.rows if len(r) >= 9 and r[3].replace(".", "").isdigit()]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": reasons}
+
+
+# --------------------------------------------------------------------------- workloads
+class GemmWorkload:
+    """bf16 GEMM C = A.B, A [M,K] row-major, B column-major, N(0,1)/sqrt(K) entries."""
+    bound = "tensor"
+
+    def __init__(self, name, M, N, K):
+        self.name, self.M, self.N, self.K = name, M, N, K
+        self.flop = 2.0 * M * N * K
+        self.bytes = 2.0 * (M * K + N * K + M * N)
+        self.metric, self.unit = "bf16_gemm_tflops", "TFLOP/s"
+        self.desc = f"bf16 GEMM M={M} N={N} K={K}, A row-major, B column-major, fp32 accumulate, bf16 out"
+        if name == "skinny":
+            self.bound = "hbm"
+
+    def host_inputs(self, rank):
+        import oracle
+        s = SEED + 1000 * rank
+        A = oracle.to_bf16_bits(oracle.normal((self.M, self.K), s + 1, 0.0, self.K ** -0.5))
+        Bt = oracle.to_bf16_bits(oracle.normal((self.N, self.K), s + 2, 0.0, self.K ** -0.5))
+        return A, Bt
+
+    def setup(self, ctx, rank, pinned):
+        A, Bt = self.host_inputs(rank)
+        self.hA, self.hB = pinned(A), pinned(Bt)
+        self.hC = pinned(np.empty((self.M, self.N), np.uint16))
+        self.dA, self.dB = ctx.upload(A), ctx.upload(Bt)
+        self.dC = ctx.empty((self.M, self.N))
+        self.h2d, self.d2h = A.nbytes + Bt.nbytes, self.hC.nbytes
+        # the working set (A + B + C) must exceed the 126 MB L2 or L2 is flushed per step
+        self.flush = None
+        if self.bytes < 2 * 126e6:
+            self.flush = ctx.empty((160 * 1024 * 1024,), 1)
+        self.flush_note = ("inputs larger than L2 (A+B+C = %.0f MB)" % (self.bytes / 1e6) if self.flush is None
+                           else "L2 flushed between steps by a 320 MB add over a scratch buffer")
+
+    def step(self, ctx):
+        if self.flush is not None:
+            ctx.add(self.flush, self.flush, self.flush)
+        ctx.matmul(self.dA, self.dB.T, out=self.dC)
+
+    kernels_per_step = property(lambda self: 1 if self.flush is None else 2)
+
+    def step_e2e(self, ctx):
+        import ctypes as C
+        from habu_b200 import model_ir
+        st = model_ir._lib.hb_matmul_host(ctx._h, self.hA.ctypes.data_as(C.c_void_p), self.hB.ctypes.data_as(C.c_void_p),
+                                          self.hC.ctypes.data_as(C.c_void_p), self.M, self.N, self.K, 1)
+        ctx._check(st)
+
+    def cpu_sample(self, max_rows=4096):
+        """Bounded CPU sample: the first `rows` rows of the same GEMM on the oracle."""
+        import oracle
+        rows = min(self.M, max_rows)
+        A = oracle.round_bf16(oracle.normal((rows, self.K), SEED + 1, 0.0, self.K ** -0.5))
+        Bt = oracle.round_bf16(oracle.normal((self.N, self.K), SEED + 2, 0.0, self.K ** -0.5))
+        t0 = time.perf_counter()
+        oracle.gemm(A, Bt.T)
+        dt = time.perf_counter() - t0
+        return 2.0 * rows * self.N * self.K / dt / 1e12, f"first {rows} of {self.M} rows of C (oracle GEMM, fp32)"
+
+
+WORKLOADS = {
+    "gemm": lambda: GemmWorkload("gemm", 8192, 8192, 8192),
+    "gemm4096": lambda: GemmWorkload("gemm4096", 4096, 4096, 4096),
+    "gemm1024": lambda: GemmWorkload("gemm1024", 1024, 1024, 1024),
+    "skinny": lambda: GemmWorkload("skinny", 16, 8192, 8192),
+}
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the CPU oracle (port) on all host threads, bounded sample per step."""
+    if rank != 0:
+        return
+    import oracle
+    wl = WORKLOADS[args.workload]()
+    vals = []
+    sample = ""
+    for i in range(args.warmup + args.steps):
+        v, sample = wl.cpu_sample(max_rows=1024)
+        if i >= args.warmup:
+            vals.append(v)
+    v = float(np.mean(vals))
+    line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl.desc},
+            "cpu_baseline": {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
+                             "sample": sample + "; the reference project has no implementation of this path"},
+            "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="gemm", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import habu_b200 as hb
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = hb.Context(local_rank)
+    stream = torch.cuda.Stream()
+    ctx.set_stream(stream.cuda_stream)
+
+    def pinned(a: np.ndarray) -> np.ndarray:
+        t = torch.empty(a.shape, dtype={2: torch.int16, 4: torch.float32}[a.dtype.itemsize]).pin_memory()
+        out = t.numpy().view(a.dtype)
+        out[...] = a
+        pinned.keep.append(t)
+        return out
+    pinned.keep = []
+
+    wl = WORKLOADS[args.workload]()
+    wl.setup(ctx, rank, pinned)
+
+    def barrier():
+        ctx.sync()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            fn(ctx)
+        e1.record(stream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident leg
+    for _ in range(args.warmup):
+        wl.step(ctx)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = ctx.launches
+    total_ms = timed(wl.step, args.steps)
+    launches = ctx.launches - l0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = total_ms / args.steps
+
+    # ---- the dominant kernel alone (no flush kernel between launches), same stream
+    kern_ms = ms_per_step
+    if wl.flush is not None:
+        def only_kernel(c):
+            c.matmul(wl.dA, wl.dB.T, out=wl.dC)
+        # rotate nothing: report the step-timed figure minus the flush, measured directly
+        flush_ms = timed(lambda c: c.add(wl.flush, wl.flush, wl.flush), args.steps) / args.steps
+        kern_ms = max(ms_per_step - flush_ms, 1e-6)
+
+    # ---- end-to-end leg through the host-buffer entry point
+    e2e_steps = max(3, min(args.steps, 10))
+    wl.step_e2e(ctx)
+    e2e_ms = timed(wl.step_e2e, e2e_steps) / e2e_steps
+
+    pk = peaks()
+    value = wl.flop * world / (kern_ms * 1e-3) / 1e12
+    e2e_value = wl.flop * world / (e2e_ms * 1e-3) / 1e12
+    long_run = total_ms > 1000.0
+    if wl.bound == "tensor":
+        peak = pk["bf16_sustained"] if long_run else pk["bf16_burst"]
+        achieved = wl.flop / (kern_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_kind": ("sustained" if long_run else "burst") + " cuBLAS bf16, of " + pk["source"]}
+    else:
+        achieved = wl.bytes / (kern_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s", "frac": achieved / pk["hbm"],
+                "peak_kind": "STREAM-style copy, of " + pk["source"]}
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(wl.name)
+    roof["kernel"] = "hb_gemm_bf16_kernel"
+    roof["kernel_ms"] = kern_ms
+
+    if rank == 0:
+        line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": wl.desc, "parallelism": "replicas only" if world > 1 else "single GPU",
+                           "l2": wl.flush_note, "seed": SEED},
+                "roofline": roof,
+                "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
+                        "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms},
+                "gpu_launches": launches, "clocks": clocks}
+        if world == 1 and not args.no_cpu_baseline:
+            import oracle
+            v, sample = wl.cpu_sample()
+            line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,6 +1,7 @@
-// fp32 GEMM on CUDA cores: C[M,N] = A[M,K] . B[K,N], fp32 storage and accumulation
-// (a single-pass TF32 tensor-core product would miss the 1e-4 relative tolerance this
-// path is held to).  64 x 64 output tile per CTA, 16 x 16 threads, 4 x 4 outputs per
+// fp32 GEMM on CUDA cores: C[M,N] = A[M,K] . B[K,N], fp32 storage; products are exact in
+// double and are accumulated in double, so the only rounding is the final store (a
+// single-pass TF32 tensor-core product, or fp32 accumulation where the sum cancels, would
+// miss the 1e-4 relative tolerance this path is held to).  64 x 64 output tile per CTA, 16 x 16 threads, 4 x 4 outputs per
 // thread, 16-wide k-slices staged in shared memory.  Operands are addressed through
 // (row stride, column stride) pairs, so row- and column-major inputs share one kernel.
 #include "hb_internal.h"
@@ -17,7 +18,7 @@ hb_gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
   __shared__ float sB[TK][T + 1];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int m0 = blockIdx.y * T, n0 = blockIdx.x * T;
-  float acc[4][4] = {};
+  double acc[4][4] = {};
   for (int k0 = 0; k0 < K; k0 += TK) {
     for (int i = threadIdx.x; i < T * TK; i += 256) {
       const int r = i / TK, kk = i % TK;   // A tile element (m0+r, k0+kk)
@@ -37,7 +38,7 @@ hb_gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) acc[i][j] = fma((double)a[i], (double)b[j], acc[i][j]);
     }
     __syncthreads();
   }
@@ -48,7 +49,7 @@ hb_gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, flo
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int gn = n0 + tx * 4 + j;
-      if (gn < N) C[gm * ldc + gn] = acc[i][j];
+      if (gn < N) C[gm * ldc + gn] = (float)acc[i][j];
     }
   }
 }

@@ -9,7 +9,7 @@ import pytest
 
 import habu_b200 as hb
 import oracle
-from util import SEED, bf16_normal, max_abs, max_rel
+from util import SEED, bf16_close, bf16_normal, max_abs, max_rel
 
 pytestmark = pytest.mark.gpu
 TOL_BF16 = 2e-2
@@ -67,10 +67,11 @@ def test_bf16_mn_major_operands(ctx, a_mn, b_mn):
 
 @pytest.mark.parametrize("epi", [hb.HB_EPI_GELU, hb.HB_EPI_SWIGLU, hb.HB_EPI_RESIDUAL])
 def test_bf16_epilogues(ctx, epi):
+    # epilogue outputs reach |x| ~ 10, where one bf16 rounding alone exceeds 2e-2
     got, ref = run_bf16(ctx, 256, 512, 256, epilogue=epi)
-    assert max_abs(got, ref) < TOL_BF16
+    assert bf16_close(got, ref) < 0
     got, ref = run_bf16(ctx, 100, 200, 64, epilogue=epi)
-    assert max_abs(got, ref) < TOL_BF16
+    assert bf16_close(got, ref) < 0
 
 
 def test_bf16_many_tiles_persistent_schedule(ctx):

@@ -16,6 +16,13 @@ def max_abs(a, b):
     return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64))))
 
 
+def bf16_close(got, ref, atol=2e-2):
+    """Largest excess over the bf16-path tolerance: max-abs `atol` against the fp32
+    reference, widened by one bf16 output rounding (2^-8 relative) where |ref| is large."""
+    ref = ref.astype(np.float64)
+    return float(np.max(np.abs(got.astype(np.float64) - ref) - (atol + np.abs(ref) * 2.0 ** -8)))
+
+
 def max_rel(a, ref, eps=1e-3):
     """|a-ref| / max(|ref|, eps*max|ref|): relative error with a floor so that entries
     that cancel to ~0 are judged against the scale of the matrix."""
