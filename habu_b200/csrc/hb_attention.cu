@@ -1,0 +1,456 @@
+// Fused causal attention forward for sm_100a, head_dim 128, bf16 in/out.
+//   O = softmax(scale * Q K^T + mask) V per (batch, head); fp32 scores, fp32 running
+//   max / sum, P rounded to bf16 for the PV product, output normalised once at the end.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong so
+// the tensor core works on one tile while the other is in its softmax.
+//   warps 0..3   softmax of tile 0: one thread per query row (= one TMEM lane).  Reads the
+//   warps 4..7   softmax of tile 1  S row with tcgen05.ld, keeps max / sum in registers,
+//                writes P (bf16) back over S with tcgen05.st, rescales O in TMEM only
+//                when the row max grew by more than 2^8 (lazy rescale), and finally
+//                normalises and stores O.
+//   warp 8       TMA producer: Q once, then K and V tiles through two-deep rings.
+//   warp 9       MMA issuer: S = Q K^T (both operands K-major in shared memory) and
+//                O += P V (P from tensor memory, V MN-major in shared memory).
+// Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t
+// aliases the first 64 columns of S_t.  tcgen05.mma executes in issue order, so the
+// commit that publishes S_t(j) also proves O_t += P_t V (j-1) has finished.
+//
+// Algorithmic work (causal): 4 * B * H * S^2 * D / 2 flop; traffic (Q + K + V + O) * 2 B.
+#include <math.h>
+
+#include "hb_internal.h"
+#include "hb_ptx.cuh"
+
+namespace {
+
+using namespace hb;
+
+constexpr int D = 128;           // head_dim
+constexpr int BQ = 128;          // query rows per tile (two tiles per CTA)
+constexpr int BKV = 128;         // keys per KV tile
+constexpr int KV_STAGES = 2;
+constexpr int ATTN_THREADS = 320;
+constexpr int TILE_BYTES = BQ * D * 2;        // 32 KB: two 128-byte-swizzled boxes of 64 columns
+constexpr int HALF_BYTES = TILE_BYTES / 2;    // one box: 128 rows x 128 B
+constexpr float RESCALE_THRESHOLD = 8.0f;     // in log2 units
+
+struct AttnParams {
+  __nv_bfloat16* O;
+  float* lse;
+  int B, S, Hq, Hkv;
+  int64_t o_sb, o_ss, o_sh;     // O strides (elements) for batch, seq, head
+  int causal;
+  float scale_log2;             // scale * log2(e)
+  float scale;
+  int n_qblocks;                // ceil(S / 256)
+  int32_t* status;
+};
+
+struct Smem {
+  static constexpr int OFF_Q = 0;                                   // 2 tiles
+  static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;              // KV_STAGES tiles
+  static constexpr int OFF_V = OFF_K + KV_STAGES * TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_V + KV_STAGES * TILE_BYTES;
+  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_full[2]
+  static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6;
+  static constexpr int OFF_TMEM_PTR = OFF_BAR + NUM_BARS * 8;
+  static constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
+  static constexpr int TOTAL = OFF_ABORT + 4;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+__global__ void __launch_bounds__(ATTN_THREADS, 1)
+hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base + Smem::OFF_Q;
+  const uint32_t sK = smem_base + Smem::OFF_K;
+  const uint32_t sV = smem_base + Smem::OFF_V;
+  const uint32_t bar0 = smem_base + Smem::OFF_BAR;
+  const uint32_t bar_q_full = bar0;
+  const uint32_t bar_k_full = bar0 + 8;
+  const uint32_t bar_k_empty = bar_k_full + KV_STAGES * 8;
+  const uint32_t bar_v_full = bar_k_empty + KV_STAGES * 8;
+  const uint32_t bar_v_empty = bar_v_full + KV_STAGES * 8;
+  const uint32_t bar_s_full = bar_v_empty + KV_STAGES * 8;
+  const uint32_t bar_p_ready = bar_s_full + 2 * 8;
+  const uint32_t bar_o_full = bar_p_ready + 2 * 8;
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + Smem::OFF_TMEM_PTR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::OFF_ABORT);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Work unit: heavy (late) query blocks of a head first; the blocks of one head run
+  // together so its K/V stay in L2.
+  const int bh = blockIdx.x / p.n_qblocks;
+  const int qblk = p.n_qblocks - 1 - (blockIdx.x % p.n_qblocks);
+  const int b = bh / p.Hq;
+  const int h = bh % p.Hq;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qblk * 2 * BQ;              // first query row of tile 0
+  // Number of KV tiles each query tile visits.
+  const int n_all = (p.S + BKV - 1) / BKV;
+  int n_t[2];
+  if (p.causal) {
+    n_t[0] = min(n_all, (q0 + BQ + BKV - 1) / BKV);
+    n_t[1] = min(n_all, (q0 + 2 * BQ + BKV - 1) / BKV);
+  } else {
+    n_t[0] = n_t[1] = n_all;
+  }
+  const bool tile1_live = (q0 + BQ) < p.S;   // tile 1 may lie wholly past the sequence
+  if (!tile1_live) n_t[1] = 0;
+  const int n_max = max(n_t[0], n_t[1]);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(bar_k_full + s * 8, 1);
+      mbar_init(bar_k_empty + s * 8, 1);
+      mbar_init(bar_v_full + s * 8, 1);
+      mbar_init(bar_v_empty + s * 8, 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar_s_full + t * 8, 1);
+      mbar_init(bar_p_ready + t * 8, 128);
+      mbar_init(bar_o_full + t * 8, 1);
+    }
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 9) {
+    tmem_alloc<1>(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), 512);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      bool ok = true;
+      mbar_arrive_expect_tx(bar_q_full, (tile1_live ? 2 : 1) * TILE_BYTES);
+      for (int t = 0; t < (tile1_live ? 2 : 1); ++t)
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(sQ + t * TILE_BYTES + c * HALF_BYTES, &tmQ, bar_q_full, c * 64, h, q0 + t * BQ, b);
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        if (!mbar_wait(bar_k_empty + s * 8, ph ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(bar_k_full + s * 8, TILE_BYTES);
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(sK + s * TILE_BYTES + c * HALF_BYTES, &tmK, bar_k_full + s * 8, c * 64, hk, j * BKV, b);
+        if (!mbar_wait(bar_v_empty + s * 8, ph ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(bar_v_full + s * 8, TILE_BYTES);
+        for (int c = 0; c < 2; ++c)
+          tma_load_4d(sV + s * TILE_BYTES + c * HALF_BYTES, &tmV, bar_v_full + s * 8, c * 64, hk, j * BKV, b);
+      }
+      if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_ATTN; p.status[2] = 1; }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc_qk = umma_idesc_bf16(BQ, BKV, 0, 0);
+      const uint32_t idesc_pv = umma_idesc_bf16(BQ, D, 0, 1);
+      bool ok = true;
+      auto issue_qk = [&](int t, int j) {
+        const int s = j % KV_STAGES;
+        const uint32_t d_tmem = tmem_base + t * 128;
+        const uint32_t a_addr = sQ + t * TILE_BYTES;
+        const uint32_t b_addr = sK + s * TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          umma_ss<1>(d_tmem, umma_desc_k_sw128(a_addr + off), umma_desc_k_sw128(b_addr + off), idesc_qk,
+                     kk != 0 ? 1u : 0u);
+        }
+        umma_commit<1>(bar_s_full + t * 8);
+      };
+      auto issue_pv = [&](int t, int j) {
+        const int s = j % KV_STAGES;
+        const uint32_t d_tmem = tmem_base + 256 + t * 128;
+        const uint32_t a_tmem = tmem_base + t * 128;     // P aliases S: 64 packed columns
+        const uint32_t b_addr = sV + s * TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          umma_ts(d_tmem, a_tmem + kk * 8, umma_desc_mn_sw128(b_addr + kk * 2048, HALF_BYTES, 1024), idesc_pv,
+                  (j | kk) != 0 ? 1u : 0u);
+      };
+      if (!mbar_wait(bar_q_full, 0, abort_flag)) ok = false;
+      // Prologue: S_t(0) for both tiles.
+      if (ok && n_max > 0) {
+        if (!mbar_wait(bar_k_full, 0, abort_flag)) ok = false;
+        if (ok) {
+          tc_fence_after();
+          issue_qk(0, 0);
+          if (n_t[1] > 0) issue_qk(1, 0);
+          umma_commit<1>(bar_k_empty);   // K(0) is free once both S(0) products have read it
+        }
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        const int sn = (j + 1) % KV_STAGES;
+        const uint32_t phn = ((j + 1) / KV_STAGES) & 1;
+        bool k_next_waited = false;
+        if (!mbar_wait(bar_v_full + s * 8, ph, abort_flag)) { ok = false; break; }
+        for (int t = 0; t < 2; ++t) {
+          if (j < n_t[t]) {
+            if (!mbar_wait(bar_p_ready + t * 8, j & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, j);
+            if (j + 1 == n_t[t]) umma_commit<1>(bar_o_full + t * 8);
+          }
+          if (j + 1 < n_t[t]) {
+            if (!k_next_waited) {
+              if (!mbar_wait(bar_k_full + sn * 8, phn, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              k_next_waited = true;
+            }
+            issue_qk(t, j + 1);
+          }
+        }
+        if (!ok) break;
+        umma_commit<1>(bar_v_empty + s * 8);
+        if (j + 1 < n_max) umma_commit<1>(bar_k_empty + sn * 8);
+      }
+      if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_ATTN; p.status[2] = 2; }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int t = warp >> 2;                    // query tile of this warpgroup
+    const int qd = warp & 3;                    // TMEM lane quarter
+    const int r = qd * 32 + lane;               // row within the tile
+    const int row = q0 + t * BQ + r;            // global query row
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
+    const uint32_t tS = tmem_base + lane_off + t * 128;
+    const uint32_t tO = tmem_base + lane_off + 256 + t * 128;
+    float m_ref = -INFINITY;                    // reference max (raw score units)
+    float l = 0.f;                              // running sum of exp2
+    bool ok = true;
+    const int n_mine = n_t[t];
+    for (int j = 0; j < n_mine && ok; ++j) {
+      if (!mbar_wait(bar_s_full + t * 8, j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t(&chunk)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]);
+        tmem_ld_32x32(tS + c * 32, chunk);
+      }
+      tmem_wait_ld();
+      // Mask: keys past the sequence end, and (diagonal tile) keys after this query.
+      const int k0 = j * BKV;
+      int limit = p.S - 1 - k0;
+      if (p.causal) limit = min(limit, row - k0);
+      if (limit < BKV - 1) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i > limit) sv[i] = 0xff800000u;   // -inf
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // Lazy rescale: move the reference max only when it would grow by more than 2^8.
+      bool need = (m_tile - m_ref) * p.scale_log2 > RESCALE_THRESHOLD;   // true on the first tile
+      if (m_tile == -INFINITY) need = false;
+      float factor = 1.0f;
+      if (need) {
+        factor = (m_ref == -INFINITY) ? 0.0f : ex2_approx((m_ref - m_tile) * p.scale_log2);
+        m_ref = m_tile;
+        l *= factor;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        // O_t += P V (j-1) has completed (see header); rescale this warp's 32 rows.
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(tO + c * 32, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * factor);
+          tmem_st_32x32(tO + c * 32, ov);
+        }
+      }
+      const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref * p.scale_log2;
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float e0 = ex2_approx(fmaf(__uint_as_float(sv[c * 16 + 2 * i]), p.scale_log2, neg_m));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(sv[c * 16 + 2 * i + 1]), p.scale_log2, neg_m));
+          l0 += e0;
+          l1 += e1;
+          pk[i] = pack_bf16x2(e0, e1);
+        }
+        // 8 packed columns = 16 keys
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};" ::"r"(pk[0]),
+                     "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]),
+                     "r"(tS + c * 8)
+                     : "memory");
+      }
+      l += l0 + l1;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p_ready + t * 8);
+    }
+    // ---- epilogue: O / l -> bf16 -> global
+    if (ok && n_mine > 0) {
+      if (!mbar_wait(bar_o_full + t * 8, 0, abort_flag)) ok = false;
+    }
+    if (ok && n_mine > 0) {
+      tc_fence_after();
+      const float inv_l = 1.0f / l;
+      __nv_bfloat16* dst = p.O + b * p.o_sb + static_cast<int64_t>(row) * p.o_ss + h * p.o_sh;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t ov[32];
+        tmem_ld_32x32(tO + c * 32, ov);
+        tmem_wait_ld();
+        if (row < p.S) {
+          uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(ov[8 * i + 0]) * inv_l, __uint_as_float(ov[8 * i + 1]) * inv_l);
+            o.y = pack_bf16x2(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
+            o.z = pack_bf16x2(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
+            o.w = pack_bf16x2(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
+            d4[i] = o;
+          }
+        }
+      }
+      if (p.lse && row < p.S)
+        p.lse[(static_cast<int64_t>(b) * p.Hq + h) * p.S + row] = m_ref * p.scale + logf(l);
+    }
+    if (!ok && p.status && lane == 0) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_ATTN; p.status[2] = 3; }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
+hb_status make_qkv_map(hb_ctx* ctx, CUtensorMap* m, const hb_tensor* t) {
+  // dims innermost first: (D, H, S, B); box (64, 1, 128, 1)
+  uint64_t dims[4] = {(uint64_t)t->shape[3], (uint64_t)t->shape[2], (uint64_t)t->shape[1], (uint64_t)t->shape[0]};
+  uint64_t strides[3] = {(uint64_t)t->stride[2] * 2, (uint64_t)t->stride[1] * 2, (uint64_t)t->stride[0] * 2};
+  uint32_t box[4] = {64, 1, 128, 1};
+  return hb_make_tensor_map(ctx, m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t->ptr, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+extern "C" hb_status hb_attention(hb_ctx* ctx, const hb_tensor* Q, const hb_tensor* K, const hb_tensor* V,
+                                  hb_tensor* O, const hb_attn_opts* opts) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!Q || !K || !V || !O || !opts) return hb_fail(ctx, HB_ERR_INVALID, "attention: null argument");
+  const hb_tensor* ts[4] = {Q, K, V, O};
+  for (const hb_tensor* t : ts) {
+    if (t->rank != 4) return hb_fail(ctx, HB_ERR_INVALID, "attention: tensors must be [batch, seq, heads, head_dim]");
+    if (t->dtype != HB_BF16) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention: only bf16 is supported");
+    if (!t->ptr) return hb_fail(ctx, HB_ERR_INVALID, "attention: null data pointer");
+    if (t->stride[3] != 1) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention: head_dim must be contiguous");
+    if ((t->stride[0] | t->stride[1] | t->stride[2]) & 7)
+      return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention: strides must be multiples of 8 elements");
+    if (reinterpret_cast<uintptr_t>(t->ptr) & 15)
+      return hb_fail(ctx, HB_ERR_INVALID, "attention: data pointers must be 16-byte aligned");
+  }
+  const int64_t B = Q->shape[0], S = Q->shape[1], Hq = Q->shape[2], Dh = Q->shape[3];
+  const int64_t Hkv = K->shape[2];
+  if (Dh != D) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention: head_dim must be 128 (got %lld)", (long long)Dh);
+  if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0) return hb_fail(ctx, HB_ERR_INVALID, "attention: empty dimension");
+  if (Hq % Hkv) return hb_fail(ctx, HB_ERR_INVALID, "attention: %lld query heads not a multiple of %lld KV heads",
+                               (long long)Hq, (long long)Hkv);
+  if (K->shape[0] != B || K->shape[1] != S || K->shape[3] != D || V->shape[0] != B || V->shape[1] != S ||
+      V->shape[2] != Hkv || V->shape[3] != D)
+    return hb_fail(ctx, HB_ERR_INVALID, "attention: K and V must be [batch, seq, kv_heads, 128]");
+  for (int i = 0; i < 4; ++i)
+    if (O->shape[i] != Q->shape[i]) return hb_fail(ctx, HB_ERR_INVALID, "attention: O must be shaped like Q");
+  if (!(opts->scale > 0.f) || !isfinite(opts->scale))
+    return hb_fail(ctx, HB_ERR_INVALID, "attention: scale must be positive and finite");
+  if (S > (1 << 24)) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention: sequence too long");
+
+  CUtensorMap tmQ, tmK, tmV;
+  hb_status st;
+  if ((st = make_qkv_map(ctx, &tmQ, Q)) != HB_OK) return st;
+  if ((st = make_qkv_map(ctx, &tmK, K)) != HB_OK) return st;
+  if ((st = make_qkv_map(ctx, &tmV, V)) != HB_OK) return st;
+
+  AttnParams p;
+  p.O = static_cast<__nv_bfloat16*>(O->ptr);
+  p.lse = static_cast<float*>(opts->lse);
+  p.B = (int)B; p.S = (int)S; p.Hq = (int)Hq; p.Hkv = (int)Hkv;
+  p.o_sb = O->stride[0]; p.o_ss = O->stride[1]; p.o_sh = O->stride[2];
+  p.causal = opts->causal ? 1 : 0;
+  p.scale = opts->scale;
+  p.scale_log2 = opts->scale * 1.4426950408889634f;
+  p.n_qblocks = (int)((S + 2 * BQ - 1) / (2 * BQ));
+  p.status = ctx->d_status;
+  const int64_t grid = B * Hq * p.n_qblocks;
+  if (grid > INT32_MAX) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention: too many work units");
+
+  static bool attr_set[64] = {};
+  if (!attr_set[ctx->device & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(hb_attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Smem::DYN_BYTES);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(attention)");
+    attr_set[ctx->device & 63] = true;
+  }
+  hb_attention_fwd_kernel<<<(unsigned)grid, ATTN_THREADS, Smem::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "attention launch");
+}
+
+extern "C" hb_status hb_attention_host(hb_ctx* ctx, const void* Q, const void* K, const void* V, void* O,
+                                       int64_t batch, int64_t seq, int64_t n_q_heads, int64_t n_kv_heads,
+                                       int64_t head_dim, int32_t causal, float scale) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!Q || !K || !V || !O) return hb_fail(ctx, HB_ERR_INVALID, "attention_host: null buffer");
+  if (batch <= 0 || seq <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0)
+    return hb_fail(ctx, HB_ERR_INVALID, "attention_host: empty dimension");
+  const size_t q_b = (size_t)batch * seq * n_q_heads * head_dim * 2;
+  const size_t kv_b = (size_t)batch * seq * n_kv_heads * head_dim * 2;
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  void* base = nullptr;
+  hb_status st = hb_get_scratch(ctx, HB_SCRATCH_STAGING, 2 * up(q_b) + 2 * up(kv_b), &base);
+  if (st != HB_OK) return st;
+  char* dQ = static_cast<char*>(base);
+  char* dK = dQ + up(q_b);
+  char* dV = dK + up(kv_b);
+  char* dO = dV + up(kv_b);
+  if ((st = hb_upload(ctx, dQ, Q, q_b)) != HB_OK) return st;
+  if ((st = hb_upload(ctx, dK, K, kv_b)) != HB_OK) return st;
+  if ((st = hb_upload(ctx, dV, V, kv_b)) != HB_OK) return st;
+  auto mk = [&](void* ptr, int64_t heads) {
+    hb_tensor t = {ptr, HB_BF16, 4, {batch, seq, heads, head_dim},
+                   {seq * heads * head_dim, heads * head_dim, head_dim, 1}};
+    return t;
+  };
+  hb_tensor tQ = mk(dQ, n_q_heads), tK = mk(dK, n_kv_heads), tV = mk(dV, n_kv_heads), tO = mk(dO, n_q_heads);
+  hb_attn_opts opts = {causal, scale, nullptr, -1};
+  if ((st = hb_attention(ctx, &tQ, &tK, &tV, &tO, &opts)) != HB_OK) return st;
+  if ((st = hb_download(ctx, O, dO, q_b)) != HB_OK) return st;
+  return hb_sync(ctx);
+}

@@ -1,8 +1,6 @@
 // Entry points still to be written; each reports HB_ERR_UNSUPPORTED.
 #include "hb_internal.h"
 #define STUB(ctx, name) return hb_fail(ctx, HB_ERR_UNSUPPORTED, name ": not built yet")
-extern "C" hb_status hb_attention(hb_ctx* ctx, const hb_tensor*, const hb_tensor*, const hb_tensor*, hb_tensor*, const hb_attn_opts*) { STUB(ctx, "attention"); }
-extern "C" hb_status hb_attention_host(hb_ctx* ctx, const void*, const void*, const void*, void*, int64_t, int64_t, int64_t, int64_t, int64_t, int32_t, float) { STUB(ctx, "attention_host"); }
 extern "C" hb_status hb_rmsnorm(hb_ctx* ctx, const void*, const void*, void*, void*, int64_t, int64_t, float) { STUB(ctx, "rmsnorm"); }
 extern "C" hb_status hb_rope(hb_ctx* ctx, void*, int64_t, int64_t, int64_t, int64_t, int64_t, float, int64_t) { STUB(ctx, "rope"); }
 extern "C" hb_status hb_embedding(hb_ctx* ctx, const void*, const int32_t*, void*, int64_t, int64_t, int64_t) { STUB(ctx, "embedding"); }

@@ -1,0 +1,124 @@
+"""GPU parity of the attention node against the CPU oracle, through the C ABI.
+
+Tolerance: max-abs 2e-2 against the oracle's fp32 attention on the same bf16-rounded
+Q, K, V (outputs are convex combinations of N(0,1) values, so O(1))."""
+import numpy as np
+import pytest
+
+import habu_b200 as hb
+import oracle
+from util import SEED, bf16_normal, max_abs
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def run(ctx, B, S, Hq, Hkv, causal=True, scale=None, lse=False):
+    D = 128
+    Q, Qb = bf16_normal((B, S, Hq, D), SEED + 31)
+    K, Kb = bf16_normal((B, S, Hkv, D), SEED + 32)
+    V, Vb = bf16_normal((B, S, Hkv, D), SEED + 33)
+    dQ, dK, dV = ctx.upload(Qb), ctx.upload(Kb), ctx.upload(Vb)
+    dL = ctx.empty((B, Hq, S), hb.HB_F32) if lse else None
+    dO = ctx.attention(dQ, dK, dV, causal=causal, scale=scale, lse=dL)
+    ctx.sync()
+    got = oracle.from_bf16_bits(ctx.download(dO))
+    ref, ref_lse = oracle.attention(Q, K, V, causal=causal, scale=scale, return_lse=True)
+    out = [got, ref]
+    if lse:
+        out += [ctx.download(dL), ref_lse]
+        ctx.free(dL)
+    for t in (dQ, dK, dV, dO):
+        ctx.free(t)
+    return out
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (1, 256, 1, 1), (2, 512, 2, 2), (1, 1024, 4, 4)])
+def test_causal_aligned(ctx, B, S, Hq, Hkv):
+    got, ref = run(ctx, B, S, Hq, Hkv)
+    assert max_abs(got, ref) < TOL
+
+
+@pytest.mark.parametrize("S", [1, 7, 129, 300, 385, 640])
+def test_causal_ragged_sequence(ctx, S):
+    got, ref = run(ctx, 2, S, 2, 2)
+    assert max_abs(got, ref) < TOL
+
+
+@pytest.mark.parametrize("S", [128, 200, 768])
+def test_non_causal(ctx, S):
+    got, ref = run(ctx, 1, S, 2, 2, causal=False)
+    assert max_abs(got, ref) < TOL
+
+
+def test_grouped_query_heads(ctx):
+    got, ref = run(ctx, 2, 512, 8, 2)
+    assert max_abs(got, ref) < TOL
+
+
+def test_scale_and_lse(ctx):
+    got, ref, lse, ref_lse = run(ctx, 1, 384, 2, 1, scale=0.2, lse=True)
+    assert max_abs(got, ref) < TOL
+    assert max_abs(lse, ref_lse) < 2e-3
+
+
+def test_large_scores_exercise_lazy_rescale(ctx):
+    # scale 1.0 with N(0,1) Q, K of width 128 gives scores ~ N(0, 128): row maxima jump by
+    # far more than 2^8 between KV tiles, so the O-rescale path runs many times.
+    got, ref = run(ctx, 1, 1024, 2, 2, scale=1.0)
+    assert max_abs(got, ref) < TOL
+
+
+def test_strided_views_into_a_fused_qkv_buffer(ctx):
+    B, S, Hq, Hkv, D = 2, 256, 4, 2, 128
+    W = (Hq + 2 * Hkv) * D
+    X, Xb = bf16_normal((B * S, W), SEED + 41)
+    dX = ctx.upload(Xb)
+    def view(off, H):
+        return ctx.wrap(dX.ptr + off * 2, (B, S, H, D), stride=(S * W, W, D, 1))
+    dO = ctx.attention(view(0, Hq), view(Hq * D, Hkv), view((Hq + Hkv) * D, Hkv))
+    ctx.sync()
+    got = oracle.from_bf16_bits(ctx.download(dO))
+    X4 = X.reshape(B, S, W)
+    Q = np.ascontiguousarray(X4[:, :, :Hq * D]).reshape(B, S, Hq, D)
+    K = np.ascontiguousarray(X4[:, :, Hq * D:(Hq + Hkv) * D]).reshape(B, S, Hkv, D)
+    V = np.ascontiguousarray(X4[:, :, (Hq + Hkv) * D:]).reshape(B, S, Hkv, D)
+    assert max_abs(got, oracle.attention(Q, K, V)) < TOL
+    ctx.free(dX)
+    ctx.free(dO)
+
+
+def test_full_size_config_sampled_heads(ctx):
+    # batch 8, 32 heads, seq 4096, head_dim 128: the oracle checks two (batch, head) pairs
+    # in full; the host-buffer entry point must agree bit for bit with the device one.
+    B, S, H, D = 8, 4096, 32, 128
+    Q, Qb = bf16_normal((B, S, H, D), SEED + 51)
+    K, Kb = bf16_normal((B, S, H, D), SEED + 52)
+    V, Vb = bf16_normal((B, S, H, D), SEED + 53)
+    dQ, dK, dV = ctx.upload(Qb), ctx.upload(Kb), ctx.upload(Vb)
+    dO = ctx.attention(dQ, dK, dV)
+    ctx.sync()
+    got = oracle.from_bf16_bits(ctx.download(dO))
+    for (b, h) in [(0, 0), (7, 31)]:
+        sl = lambda X: np.ascontiguousarray(X[b:b + 1, :, h:h + 1, :])
+        ref = oracle.attention(sl(Q), sl(K), sl(V))
+        assert max_abs(got[b:b + 1, :, h:h + 1, :], ref) < TOL
+    # softmax rows are convex weights: every output lies within the range of V seen so far
+    assert np.all(np.abs(got) <= np.abs(V).max() + 1e-2)
+    host = oracle.from_bf16_bits(ctx.attention_host(Qb, Kb, Vb))
+    assert np.array_equal(host, got)
+    for t in (dQ, dK, dV, dO):
+        ctx.free(t)
+
+
+def test_invalid_arguments(ctx):
+    q = ctx.empty((1, 128, 3, 128))
+    k = ctx.empty((1, 128, 2, 128))
+    with pytest.raises(hb.HabuError) as e:
+        ctx.attention(q, k, k)          # 3 query heads over 2 KV heads
+    assert e.value.status == 1
+    q64 = ctx.empty((1, 128, 2, 64))
+    with pytest.raises(hb.HabuError) as e:
+        ctx.attention(q64, q64, q64)    # head_dim 64
+    assert e.value.status == 7
+    ctx.sync()
