@@ -77,6 +77,7 @@ def load() -> C.CDLL:
         "hb_embedding": [vp, vp, vp, vp, i64, i64, i64],
         "hb_swiglu": [vp, vp, vp, i64, i64],
         "hb_gelu": [vp, vp, vp, i64],
+        "hb_gelu_backward": [vp, vp, vp, vp, i64],
         "hb_add": [vp, vp, vp, vp, i64],
         "hb_argmax": [vp, vp, vp, i64, i64],
         "hb_comm_unique_id": [vp],

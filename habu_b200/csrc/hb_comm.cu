@@ -1,0 +1,354 @@
+// Collective node: sum-allreduce across the GPUs of one box.
+//
+//   HB_AR_NCCL  ncclAllReduce enqueued on the context's stream.  NCCL is bound at run time
+//               (dlopen of the libnccl.so.2 already in the process, else the system one), so
+//               the library neither links NCCL nor pulls a second copy into a host process
+//               that already carries one.
+//   HB_AR_P2P   this library's two-shot kernel over peer-mapped buffers (NVLink through
+//               NVSwitch): every rank owns 1/world of the elements, READS that slice from
+//               each peer with plain loads, adds in rank order in fp32, and WRITES the sum
+//               into every rank's buffer with plain stores.  Each CTA handshakes only with
+//               the same-numbered CTA of the peers (flag words in the symmetric buffer,
+//               release/acquire at system scope), so no CTA ever waits on another CTA of its
+//               own GPU.  Every wait is bounded: on time-out the kernel records
+//               HB_ERR_TIMEOUT and returns.  No multimem and no multicast loads are used.
+// Algorithmic bytes per rank: 2 * (world-1)/world * count * elem over NVLink.
+#include <dlfcn.h>
+#include <nccl.h>
+#include <string.h>
+
+#include "hb_internal.h"
+
+namespace {
+
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
+};
+
+NcclApi* nccl_api() {
+  static NcclApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    const char* env = getenv("HB_NCCL_LIB");
+    if (!h && env) h = dlopen(env, RTLD_NOW);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW);
+    if (!h) return;
+    api.handle = h;
+#define HB_SYM(field, name) api.field = reinterpret_cast<decltype(api.field)>(dlsym(h, name))
+    HB_SYM(GetUniqueId, "ncclGetUniqueId");
+    HB_SYM(CommInitRank, "ncclCommInitRank");
+    HB_SYM(CommDestroy, "ncclCommDestroy");
+    HB_SYM(CommAbort, "ncclCommAbort");
+    HB_SYM(AllReduce, "ncclAllReduce");
+    HB_SYM(GetErrorString, "ncclGetErrorString");
+    HB_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
+#undef HB_SYM
+    if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy) api.handle = nullptr;
+  });
+  return api.handle ? &api : nullptr;
+}
+
+// ------------------------------------------------------------------ P2P two-shot kernel
+constexpr int AR_MAX_WORLD = 8;
+constexpr int AR_MAX_CTAS = 296;                       // 2 per SM on a 148-SM part
+constexpr int AR_THREADS = 512;
+constexpr size_t AR_FLAG_BYTES = 2 * AR_MAX_CTAS * AR_MAX_WORLD * sizeof(uint32_t);
+constexpr uint32_t AR_SPIN_LIMIT = 1u << 24;
+
+struct ArParams {
+  void* peers[AR_MAX_WORLD];      // base of every rank's symmetric buffer (data first)
+  size_t flag_off;                // byte offset of the flag block inside each buffer
+  size_t data_off;                // byte offset of the payload inside each buffer
+  int64_t count;                  // elements
+  int world, rank;
+  uint32_t epoch;
+  int32_t* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Handshake `phase` (0 start, 1 end) of CTA `cta` with the same CTA on every peer.
+__device__ bool ar_barrier(const ArParams& p, int phase, int cta) {
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    const int peer = threadIdx.x;
+    // my arrival, written into the peer's flag block at [phase][cta][my rank]
+    uint32_t* remote = reinterpret_cast<uint32_t*>(static_cast<char*>(p.peers[peer]) + p.flag_off) +
+                       (static_cast<size_t>(phase) * AR_MAX_CTAS + cta) * AR_MAX_WORLD + p.rank;
+    st_release_sys(remote, p.epoch);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(static_cast<char*>(p.peers[p.rank]) + p.flag_off) +
+                           (static_cast<size_t>(phase) * AR_MAX_CTAS + cta) * AR_MAX_WORLD + peer;
+    uint32_t it = 0;
+    // epochs only grow; a peer that is already one call ahead has also passed this one
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - p.epoch) < 0) {
+      if (++it > AR_SPIN_LIMIT) { failed = 1; break; }
+    }
+  }
+  __syncthreads();
+  const bool ok = failed == 0;
+  if (!ok && threadIdx.x == 0 && p.status) {
+    atomicCAS(p.status, 0, HB_ERR_TIMEOUT);
+    p.status[1] = HB_KTAG_ALLREDUCE;
+    p.status[2] = phase;
+  }
+  return ok;
+}
+
+template <typename T>
+struct Vec;   // 16-byte vector of T with fp32 accumulate helpers
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  static __device__ void add(float (&acc)[4], const uint4& v) {
+    acc[0] += __uint_as_float(v.x); acc[1] += __uint_as_float(v.y);
+    acc[2] += __uint_as_float(v.z); acc[3] += __uint_as_float(v.w);
+  }
+  static __device__ uint4 pack(const float (&acc)[4]) {
+    return make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
+  }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ void add(float (&acc)[8], const uint4& v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+      acc[2 * k] += f.x;
+      acc[2 * k + 1] += f.y;
+    }
+  }
+  static __device__ uint4 pack(const float (&acc)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+      w[k] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(AR_THREADS)
+hb_allreduce_p2p_kernel(const ArParams p) {
+  constexpr int N = Vec<T>::N;
+  const int cta = blockIdx.x;
+  if (!ar_barrier(p, 0, cta)) return;
+  // Slice owned by this rank, in 16-byte vectors; the tail (count % N) is handled by rank 0.
+  const int64_t nvec = p.count / N;
+  const int64_t per = (nvec + p.world - 1) / p.world;
+  const int64_t v0 = per * p.rank;
+  const int64_t v1 = min(nvec, v0 + per);
+  const uint4* src[AR_MAX_WORLD];
+  uint4* dst[AR_MAX_WORLD];
+#pragma unroll
+  for (int r = 0; r < AR_MAX_WORLD; ++r) {
+    src[r] = r < p.world ? reinterpret_cast<const uint4*>(static_cast<char*>(p.peers[r]) + p.data_off) : nullptr;
+    dst[r] = const_cast<uint4*>(src[r]);
+  }
+  for (int64_t i = v0 + cta * (int64_t)AR_THREADS + threadIdx.x; i < v1; i += (int64_t)gridDim.x * AR_THREADS) {
+    uint4 v[AR_MAX_WORLD];
+#pragma unroll
+    for (int r = 0; r < AR_MAX_WORLD; ++r)
+      if (r < p.world) v[r] = src[r][i];           // peer loads over NVLink, all in flight
+    float acc[N] = {};
+#pragma unroll
+    for (int r = 0; r < AR_MAX_WORLD; ++r)
+      if (r < p.world) Vec<T>::add(acc, v[r]);      // fixed rank order: identical on every rank
+    const uint4 out = Vec<T>::pack(acc);
+#pragma unroll
+    for (int r = 0; r < AR_MAX_WORLD; ++r)
+      if (r < p.world) dst[r][i] = out;
+  }
+  if (p.rank == 0 && cta == 0 && threadIdx.x < (int)(p.count % N)) {
+    const int64_t e = nvec * N + threadIdx.x;
+    float s = 0.f;
+    for (int r = 0; r < p.world; ++r) {
+      const T* q = reinterpret_cast<const T*>(static_cast<char*>(p.peers[r]) + p.data_off);
+      s += static_cast<float>(q[e]);
+    }
+    for (int r = 0; r < p.world; ++r) {
+      T* q = reinterpret_cast<T*>(static_cast<char*>(p.peers[r]) + p.data_off);
+      q[e] = static_cast<T>(s);
+    }
+  }
+  ar_barrier(p, 1, cta);
+}
+
+}  // namespace
+
+extern "C" hb_status hb_comm_unique_id(void* id_out) {
+  if (!id_out) return HB_ERR_INVALID;
+  NcclApi* api = nccl_api();
+  if (!api) return HB_ERR_NCCL;
+  static_assert(sizeof(ncclUniqueId) <= HB_UNIQUE_ID_BYTES, "unique id size");
+  ncclUniqueId id;
+  if (api->GetUniqueId(&id) != ncclSuccess) return HB_ERR_NCCL;
+  memset(id_out, 0, HB_UNIQUE_ID_BYTES);
+  memcpy(id_out, &id, sizeof(id));
+  return HB_OK;
+}
+
+extern "C" hb_status hb_comm_init_rank(hb_ctx* ctx, int32_t world, int32_t rank, const void* unique_id) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (world < 1 || rank < 0 || rank >= world) return hb_fail(ctx, HB_ERR_INVALID, "comm: rank %d of %d", rank, world);
+  if (ctx->nccl_comm) return hb_fail(ctx, HB_ERR_DUPLICATE, "comm: this context already has a communicator");
+  ctx->world = world;
+  ctx->rank = rank;
+  if (world == 1) return HB_OK;
+  if (!unique_id) return hb_fail(ctx, HB_ERR_INVALID, "comm: null unique id");
+  NcclApi* api = nccl_api();
+  if (!api) return hb_fail(ctx, HB_ERR_NCCL, "comm: libnccl.so.2 could not be loaded");
+  cudaError_t ce = cudaSetDevice(ctx->device);
+  if (ce != cudaSuccess) return hb_check_cuda(ctx, ce, "cudaSetDevice");
+  ncclUniqueId id;
+  memcpy(&id, unique_id, sizeof(id));
+  ncclComm_t comm;
+  ncclResult_t r = api->CommInitRank(&comm, world, id, rank);
+  if (r != ncclSuccess)
+    return hb_fail(ctx, HB_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString ? api->GetErrorString(r) : "error");
+  ctx->nccl_comm = comm;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_comm_destroy(hb_ctx* ctx) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (ctx->nccl_comm) {
+    NcclApi* api = nccl_api();
+    if (api) api->CommDestroy(static_cast<ncclComm_t>(ctx->nccl_comm));
+    ctx->nccl_comm = nullptr;
+  }
+  hb_p2p_state& s = ctx->p2p;
+  for (int r = 0; r < (int)s.peers.size(); ++r)
+    if (r != s.rank && s.peers[r]) cudaIpcCloseMemHandle(s.peers[r]);
+  s.peers.clear();
+  if (s.local) { cudaFree(s.local); s.local = nullptr; }
+  s.world = 0;
+  return HB_OK;
+}
+
+// The symmetric buffer holds `bytes` of payload followed by the flag block.
+extern "C" hb_status hb_p2p_alloc(hb_ctx* ctx, size_t bytes, void** dev_ptr, void* handle_out) {
+  if (!ctx || !dev_ptr || !handle_out) return HB_ERR_INVALID;
+  if (ctx->p2p.local) return hb_fail(ctx, HB_ERR_DUPLICATE, "p2p: this context already owns a symmetric buffer");
+  if (bytes == 0) return hb_fail(ctx, HB_ERR_INVALID, "p2p: empty buffer");
+  static_assert(sizeof(cudaIpcMemHandle_t) <= HB_IPC_HANDLE_BYTES, "ipc handle size");
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaSetDevice");
+  const size_t payload = (bytes + 255) & ~size_t(255);
+  void* p = nullptr;
+  e = cudaMalloc(&p, payload + AR_FLAG_BYTES);
+  if (e != cudaSuccess) { cudaGetLastError(); return hb_fail(ctx, HB_ERR_NOMEM, "p2p: cannot allocate %zu bytes", payload); }
+  e = cudaMemset(p, 0, payload + AR_FLAG_BYTES);
+  if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaMemset");
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaFree(p); return hb_check_cuda(ctx, e, "cudaIpcGetMemHandle"); }
+  memset(handle_out, 0, HB_IPC_HANDLE_BYTES);
+  memcpy(handle_out, &h, sizeof(h));
+  ctx->p2p.local = p;
+  ctx->p2p.bytes = payload;
+  *dev_ptr = p;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_p2p_attach(hb_ctx* ctx, int32_t world, int32_t rank, const void* all_handles, size_t bytes) {
+  if (!ctx || !all_handles) return HB_ERR_INVALID;
+  hb_p2p_state& s = ctx->p2p;
+  if (!s.local) return hb_fail(ctx, HB_ERR_NOT_FOUND, "p2p: call hb_p2p_alloc first");
+  if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world)
+    return hb_fail(ctx, HB_ERR_INVALID, "p2p: rank %d of %d (at most %d ranks)", rank, world, AR_MAX_WORLD);
+  if (((bytes + 255) & ~size_t(255)) != s.bytes) return hb_fail(ctx, HB_ERR_INVALID, "p2p: size differs from hb_p2p_alloc");
+  if (!s.peers.empty()) return hb_fail(ctx, HB_ERR_DUPLICATE, "p2p: already attached");
+  cudaError_t e = cudaSetDevice(ctx->device);
+  if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaSetDevice");
+  s.peers.assign(world, nullptr);
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) { s.peers[r] = s.local; continue; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const char*>(all_handles) + (size_t)r * HB_IPC_HANDLE_BYTES, sizeof(h));
+    e = cudaIpcOpenMemHandle(&s.peers[r], h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      s.peers[r] = nullptr;
+      return hb_check_cuda(ctx, e, "cudaIpcOpenMemHandle");
+    }
+  }
+  s.world = world;
+  s.rank = rank;
+  s.epoch = 0;
+  ctx->world = world;
+  ctx->rank = rank;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!data) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: null pointer");
+  if (count <= 0) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: empty tensor");
+  if (dtype != HB_BF16 && dtype != HB_F32) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "all_reduce: dtype %d", dtype);
+  if (ctx->world == 1) return HB_OK;   // a single rank already holds the sum
+  const size_t es = dtype == HB_BF16 ? 2 : 4;
+  hb_p2p_state& s = ctx->p2p;
+  const char* lo = static_cast<const char*>(s.local);
+  const bool inside = s.world > 1 && static_cast<const char*>(data) >= lo &&
+                      static_cast<const char*>(data) + (size_t)count * es <= lo + s.bytes;
+  if (algo == HB_AR_AUTO) algo = inside ? HB_AR_P2P : HB_AR_NCCL;
+  if (algo == HB_AR_NCCL) {
+    NcclApi* api = nccl_api();
+    if (!api || !ctx->nccl_comm) return hb_fail(ctx, HB_ERR_NCCL, "all_reduce: no NCCL communicator (hb_comm_init_rank)");
+    ncclResult_t r = api->AllReduce(data, data, (size_t)count, dtype == HB_BF16 ? ncclBfloat16 : ncclFloat32, ncclSum,
+                                    static_cast<ncclComm_t>(ctx->nccl_comm), ctx->stream);
+    if (r != ncclSuccess)
+      return hb_fail(ctx, HB_ERR_NCCL, "ncclAllReduce: %s", api->GetErrorString ? api->GetErrorString(r) : "error");
+    ctx->launches++;
+    return HB_OK;
+  }
+  if (algo != HB_AR_P2P) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: unknown algorithm %d", algo);
+  if (s.world < 2) return hb_fail(ctx, HB_ERR_NOT_FOUND, "all_reduce: no peer buffers attached (hb_p2p_attach)");
+  if (!inside)
+    return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: P2P needs the tensor inside the symmetric buffer of hb_p2p_alloc");
+  const size_t off = static_cast<const char*>(data) - lo;
+  if (off & 15) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: tensor must be 16-byte aligned in the symmetric buffer");
+  ArParams p;
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < s.world; ++r) p.peers[r] = s.peers[r];
+  p.flag_off = s.bytes;
+  p.data_off = off;
+  p.count = count;
+  p.world = s.world;
+  p.rank = s.rank;
+  p.epoch = ++s.epoch;
+  p.status = ctx->d_status;
+  const int64_t nvec = count / (16 / es);
+  int64_t want = (nvec / s.world + AR_THREADS - 1) / AR_THREADS;
+  int grid = (int)(want < 1 ? 1 : want);
+  const int cap = ctx->sm_count * 2 < AR_MAX_CTAS ? ctx->sm_count * 2 : AR_MAX_CTAS;
+  if (grid > cap) grid = cap;
+  if (dtype == HB_BF16)
+    hb_allreduce_p2p_kernel<__nv_bfloat16><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+  else
+    hb_allreduce_p2p_kernel<float><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "all_reduce launch");
+}

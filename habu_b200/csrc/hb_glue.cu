@@ -1,0 +1,337 @@
+// HBM-bound glue operators of the decoder / MLP configurations: RMSNorm (+ fused residual
+// add), rotate-half RoPE, embedding gather, SwiGLU, GELU (+ backward), add, argmax, MSE
+// and Adam.  bf16 storage, fp32 math, 16-byte vector accesses; every kernel moves each
+// byte once.
+#include <math.h>
+
+#include "hb_internal.h"
+
+namespace {
+
+__device__ __forceinline__ float2 bf2_to_f2(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+__device__ __forceinline__ uint32_t f2_to_bf2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One CTA per row, row held in registers (up to 8 x 16 B per thread).  Traffic per row:
+// cols * 2 B in, cols * 2 B out (+ the same again for the residual stream when fused).
+constexpr int RMS_THREADS = 256;
+constexpr int RMS_MAX_VEC = 8;   // cols <= 256 * 8 * 8 = 16384
+
+__global__ void __launch_bounds__(RMS_THREADS)
+rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain, uint4* __restrict__ y,
+               uint4* residual, int cols8, float inv_cols, float eps) {
+  __shared__ float red[RMS_THREADS / 32];
+  const int64_t row = blockIdx.x;
+  const uint4* xr = x + row * cols8;
+  uint4* rr = residual ? residual + row * cols8 : nullptr;
+  float v[RMS_MAX_VEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RMS_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * RMS_THREADS;
+    if (c < cols8) {
+      const uint4 a = xr[c];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+      uint32_t rw[4] = {0, 0, 0, 0};
+      if (rr) { const uint4 r = rr[c]; rw[0] = r.x; rw[1] = r.y; rw[2] = r.z; rw[3] = r.w; }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 f = bf2_to_f2(aw[k]);
+        if (rr) {
+          const float2 g = bf2_to_f2(rw[k]);
+          // the updated residual is what gets normalised, after its own bf16 rounding
+          rw[k] = f2_to_bf2(f.x + g.x, f.y + g.y);
+          f = bf2_to_f2(rw[k]);
+        }
+        v[i][2 * k] = f.x;
+        v[i][2 * k + 1] = f.y;
+        ss += f.x * f.x + f.y * f.y;
+      }
+      if (rr) rr[c] = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < RMS_THREADS / 32; ++w) tot += red[w];
+  const float inv = rsqrtf(tot * inv_cols + eps);
+  uint4* yr = y + row * cols8;
+#pragma unroll
+  for (int i = 0; i < RMS_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * RMS_THREADS;
+    if (c < cols8) {
+      const uint4 g = __ldg(gain + c);
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 gf = bf2_to_f2(gw[k]);
+        o[k] = f2_to_bf2(v[i][2 * k] * inv * gf.x, v[i][2 * k + 1] * inv * gf.y);
+      }
+      yr[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RoPE (rotate-half)
+// One thread per (token, head, 8 consecutive pair indices): loads 16 B from each half.
+__global__ void rope_kernel(__nv_bfloat16* x, int64_t tokens, int seq, int heads, int head_dim,
+                            int64_t row_stride, float log2_base, int64_t pos0) {
+  const int half = head_dim >> 1;
+  const int groups = half >> 3;
+  const int64_t total = tokens * heads * groups;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int g = (int)(idx % groups);
+    const int h = (int)((idx / groups) % heads);
+    const int64_t t = idx / ((int64_t)groups * heads);
+    const double pos = (double)(pos0 + t % seq);
+    __nv_bfloat16* base = x + t * row_stride + (int64_t)h * head_dim + g * 8;
+    uint4 lo = *reinterpret_cast<uint4*>(base);
+    uint4 hi = *reinterpret_cast<uint4*>(base + half);
+    uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+    uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = bf2_to_f2(lw[k]);
+      const float2 b = bf2_to_f2(hw[k]);
+      float c0, s0, c1, s1;
+      const int i0 = g * 8 + 2 * k;
+      // theta = pos * base^(-2i/d); the angle is formed in double, reduced by sincosf
+      const float th0 = (float)(pos * exp2(-2.0 * i0 / head_dim * (double)log2_base));
+      const float th1 = (float)(pos * exp2(-2.0 * (i0 + 1) / head_dim * (double)log2_base));
+      sincosf(th0, &s0, &c0);
+      sincosf(th1, &s1, &c1);
+      lw[k] = f2_to_bf2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+      hw[k] = f2_to_bf2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+    }
+    *reinterpret_cast<uint4*>(base) = lo;
+    *reinterpret_cast<uint4*>(base + half) = hi;
+  }
+}
+
+// ------------------------------------------------------------------ embedding gather
+__global__ void embedding_kernel(const uint4* __restrict__ table, const int32_t* __restrict__ ids,
+                                 uint4* __restrict__ out, int64_t tokens, int vocab, int dim8,
+                                 int32_t* status) {
+  const int64_t total = tokens * dim8;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / dim8;
+    const int c = (int)(idx % dim8);
+    const int id = ids[t];
+    if (id < 0 || id >= vocab) {   // record and skip: never read out of bounds
+      if (c == 0) { atomicCAS(status, 0, HB_ERR_INVALID); status[1] = 10; status[2] = id; }
+      out[idx] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    out[idx] = table[(int64_t)id * dim8 + c];
+  }
+}
+
+// ------------------------------------------------------------------ elementwise
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float gelu_f(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
+
+// out[r, j] = silu(x[r, j]) * x[r, half + j]; half8 = half / 8
+__global__ void swiglu_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, int64_t rows, int half8) {
+  const int64_t total = rows * half8;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / half8;
+    const int c = (int)(idx % half8);
+    const uint4 g = x[r * 2 * half8 + c], u = x[r * 2 * half8 + half8 + c];
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = bf2_to_f2(gw[k]), b = bf2_to_f2(uw[k]);
+      o[k] = f2_to_bf2(silu_f(a.x) * b.x, silu_f(a.y) * b.y);
+    }
+    out[idx] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <int OP>  // 0 gelu(x), 1 a + b, 2 gelu'(a) * b
+__global__ void ew_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out,
+                          int64_t n8, const __nv_bfloat16* at, const __nv_bfloat16* bt, __nv_bfloat16* ot,
+                          int tail) {
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < n8;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 av = a[idx];
+    uint4 bv = make_uint4(0, 0, 0, 0);
+    if (OP != 0) bv = b[idx];
+    const uint32_t aw[4] = {av.x, av.y, av.z, av.w}, bw[4] = {bv.x, bv.y, bv.z, bv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 x = bf2_to_f2(aw[k]), y = bf2_to_f2(bw[k]);
+      if (OP == 0) o[k] = f2_to_bf2(gelu_f(x.x), gelu_f(x.y));
+      else if (OP == 1) o[k] = f2_to_bf2(x.x + y.x, x.y + y.y);
+      else {
+        auto dg = [](float v) {
+          return 0.5f * (1.0f + erff(v * 0.70710678118654752f)) + v * 0.3989422804014327f * __expf(-0.5f * v * v);
+        };
+        o[k] = f2_to_bf2(dg(x.x) * y.x, dg(x.y) * y.y);
+      }
+    }
+    out[idx] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < tail) {   // last n % 8 elements
+    const float x = __bfloat162float(at[threadIdx.x]);
+    const float y = OP != 0 ? __bfloat162float(bt[threadIdx.x]) : 0.f;
+    float r;
+    if (OP == 0) r = gelu_f(x);
+    else if (OP == 1) r = x + y;
+    else r = (0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x)) * y;
+    ot[threadIdx.x] = __float2bfloat16_rn(r);
+  }
+}
+
+// ------------------------------------------------------------------ argmax (first index wins)
+__global__ void __launch_bounds__(256)
+argmax_kernel(const __nv_bfloat16* __restrict__ x, int32_t* __restrict__ out, int64_t cols) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const __nv_bfloat16* xr = x + blockIdx.x * cols;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    const float v = __bfloat162float(xr[c]);
+    if (v > bv || (v == bv && (int)c < bi)) { bv = v; bi = (int)c; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+int grid_for(hb_ctx* ctx, int64_t work_items, int threads) {
+  const int64_t want = (work_items + threads - 1) / threads;
+  const int64_t cap = (int64_t)ctx->sm_count * 8;   // a multiple of the SM count
+  return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
+}  // namespace
+
+#define HB_ALIGNED16(p) ((reinterpret_cast<uintptr_t>(p) & 15) == 0)
+
+extern "C" hb_status hb_rmsnorm(hb_ctx* ctx, const void* x, const void* gain, void* y, void* residual_inout,
+                                int64_t rows, int64_t cols, float eps) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!x || !gain || !y) return hb_fail(ctx, HB_ERR_INVALID, "rmsnorm: null pointer");
+  if (rows <= 0 || cols <= 0) return hb_fail(ctx, HB_ERR_INVALID, "rmsnorm: empty dimension");
+  if (cols % 8 || cols > RMS_THREADS * RMS_MAX_VEC * 8)
+    return hb_fail(ctx, HB_ERR_UNSUPPORTED, "rmsnorm: cols must be a multiple of 8 and at most %d",
+                   RMS_THREADS * RMS_MAX_VEC * 8);
+  if (!HB_ALIGNED16(x) || !HB_ALIGNED16(gain) || !HB_ALIGNED16(y) || !HB_ALIGNED16(residual_inout))
+    return hb_fail(ctx, HB_ERR_INVALID, "rmsnorm: pointers must be 16-byte aligned");
+  if (rows > INT32_MAX) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "rmsnorm: too many rows");
+  rmsnorm_kernel<<<(unsigned)rows, RMS_THREADS, 0, ctx->stream>>>(
+      static_cast<const uint4*>(x), static_cast<const uint4*>(gain), static_cast<uint4*>(y),
+      static_cast<uint4*>(residual_inout), (int)(cols / 8), 1.0f / (float)cols, eps);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "rmsnorm launch");
+}
+
+extern "C" hb_status hb_rope(hb_ctx* ctx, void* x, int64_t tokens, int64_t seq, int64_t heads, int64_t head_dim,
+                             int64_t row_stride, float base, int64_t pos0) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!x) return hb_fail(ctx, HB_ERR_INVALID, "rope: null pointer");
+  if (tokens <= 0 || seq <= 0 || heads <= 0 || head_dim <= 0) return hb_fail(ctx, HB_ERR_INVALID, "rope: empty dimension");
+  if (head_dim % 16 || row_stride % 8 || !HB_ALIGNED16(x))
+    return hb_fail(ctx, HB_ERR_UNSUPPORTED, "rope: head_dim must be a multiple of 16 and rows 16-byte aligned");
+  if (row_stride < heads * head_dim) return hb_fail(ctx, HB_ERR_INVALID, "rope: row stride smaller than heads * head_dim");
+  if (!(base > 1.0f)) return hb_fail(ctx, HB_ERR_INVALID, "rope: base must exceed 1");
+  const int64_t work = tokens * heads * (head_dim / 16);
+  rope_kernel<<<grid_for(ctx, work, 256), 256, 0, ctx->stream>>>(static_cast<__nv_bfloat16*>(x), tokens, (int)seq,
+                                                                 (int)heads, (int)head_dim, row_stride,
+                                                                 log2f(base), pos0);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "rope launch");
+}
+
+extern "C" hb_status hb_embedding(hb_ctx* ctx, const void* table, const int32_t* ids, void* out, int64_t tokens,
+                                  int64_t vocab, int64_t dim) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!table || !ids || !out) return hb_fail(ctx, HB_ERR_INVALID, "embedding: null pointer");
+  if (tokens <= 0 || vocab <= 0 || dim <= 0) return hb_fail(ctx, HB_ERR_INVALID, "embedding: empty dimension");
+  if (dim % 8 || !HB_ALIGNED16(table) || !HB_ALIGNED16(out) || vocab > INT32_MAX)
+    return hb_fail(ctx, HB_ERR_UNSUPPORTED, "embedding: dim must be a multiple of 8 and pointers 16-byte aligned");
+  embedding_kernel<<<grid_for(ctx, tokens * (dim / 8), 256), 256, 0, ctx->stream>>>(
+      static_cast<const uint4*>(table), ids, static_cast<uint4*>(out), tokens, (int)vocab, (int)(dim / 8),
+      ctx->d_status);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "embedding launch");
+}
+
+extern "C" hb_status hb_swiglu(hb_ctx* ctx, const void* x, void* out, int64_t rows, int64_t half) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!x || !out) return hb_fail(ctx, HB_ERR_INVALID, "swiglu: null pointer");
+  if (rows <= 0 || half <= 0) return hb_fail(ctx, HB_ERR_INVALID, "swiglu: empty dimension");
+  if (half % 8 || !HB_ALIGNED16(x) || !HB_ALIGNED16(out))
+    return hb_fail(ctx, HB_ERR_UNSUPPORTED, "swiglu: half width must be a multiple of 8 and pointers 16-byte aligned");
+  swiglu_kernel<<<grid_for(ctx, rows * (half / 8), 256), 256, 0, ctx->stream>>>(
+      static_cast<const uint4*>(x), static_cast<uint4*>(out), rows, (int)(half / 8));
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "swiglu launch");
+}
+
+template <int OP>
+static hb_status launch_ew(hb_ctx* ctx, const char* name, const void* a, const void* b, void* out, int64_t n) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!a || !out || (OP != 0 && !b)) return hb_fail(ctx, HB_ERR_INVALID, "%s: null pointer", name);
+  if (n <= 0) return hb_fail(ctx, HB_ERR_INVALID, "%s: empty tensor", name);
+  if (!HB_ALIGNED16(a) || !HB_ALIGNED16(b) || !HB_ALIGNED16(out))
+    return hb_fail(ctx, HB_ERR_INVALID, "%s: pointers must be 16-byte aligned", name);
+  const int64_t n8 = n / 8;
+  const int tail = (int)(n % 8);
+  const __nv_bfloat16* at = static_cast<const __nv_bfloat16*>(a) + n8 * 8;
+  const __nv_bfloat16* bt = b ? static_cast<const __nv_bfloat16*>(b) + n8 * 8 : nullptr;
+  __nv_bfloat16* ot = static_cast<__nv_bfloat16*>(out) + n8 * 8;
+  ew_kernel<OP><<<grid_for(ctx, n8, 256), 256, 0, ctx->stream>>>(
+      static_cast<const uint4*>(a), static_cast<const uint4*>(b), static_cast<uint4*>(out), n8, at, bt, ot, tail);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), name);
+}
+
+extern "C" hb_status hb_gelu(hb_ctx* ctx, const void* x, void* y, int64_t n) {
+  return launch_ew<0>(ctx, "gelu", x, nullptr, y, n);
+}
+extern "C" hb_status hb_add(hb_ctx* ctx, const void* a, const void* b, void* out, int64_t n) {
+  return launch_ew<1>(ctx, "add", a, b, out, n);
+}
+extern "C" hb_status hb_gelu_backward(hb_ctx* ctx, const void* x, const void* dy, void* dx, int64_t n) {
+  return launch_ew<2>(ctx, "gelu_backward", x, dy, dx, n);
+}
+
+extern "C" hb_status hb_argmax(hb_ctx* ctx, const void* x, int32_t* out, int64_t rows, int64_t cols) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!x || !out) return hb_fail(ctx, HB_ERR_INVALID, "argmax: null pointer");
+  if (rows <= 0 || cols <= 0 || rows > INT32_MAX || cols > INT32_MAX)
+    return hb_fail(ctx, HB_ERR_INVALID, "argmax: bad dimensions");
+  argmax_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(x), out, cols);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "argmax launch");
+}

@@ -1,6 +1,7 @@
 // Internal (non-ABI) declarations shared by the translation units of libhabu_b200.so.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 

@@ -233,6 +233,12 @@ class Context:
         self._check(_lib.hb_gelu(self._h, x.ptr, out.ptr, x.nbytes // 2))
         return out
 
+    def gelu_backward(self, x: Tensor, dy: Tensor, out: Optional[Tensor] = None) -> Tensor:
+        if out is None:
+            out = self.empty(x.shape, x.dtype)
+        self._check(_lib.hb_gelu_backward(self._h, x.ptr, dy.ptr, out.ptr, x.nbytes // 2))
+        return out
+
     def add(self, a: Tensor, b: Tensor, out: Optional[Tensor] = None) -> Tensor:
         if out is None:
             out = self.empty(a.shape, a.dtype)

@@ -135,6 +135,8 @@ hb_status hb_embedding(hb_ctx* ctx, const void* table, const int32_t* ids, void*
 /* out[r, j] = silu(x[r, j]) * x[r, half + j]  for x[rows, 2*half] bf16. */
 hb_status hb_swiglu(hb_ctx* ctx, const void* x, void* out, int64_t rows, int64_t half);
 hb_status hb_gelu(hb_ctx* ctx, const void* x, void* y, int64_t n);
+/* dx = dy * gelu'(x) (erf-exact derivative). */
+hb_status hb_gelu_backward(hb_ctx* ctx, const void* x, const void* dy, void* dx, int64_t n);
 hb_status hb_add(hb_ctx* ctx, const void* a, const void* b, void* out, int64_t n);
 /* argmax over the last dimension, first index wins ties (bit-exact). */
 hb_status hb_argmax(hb_ctx* ctx, const void* x, int32_t* out, int64_t rows, int64_t cols);
