@@ -51,6 +51,11 @@ class hb_tune_result(C.Structure):
                 ("tflops", C.c_float)]
 
 
+class hb_node(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("inputs", C.c_int32 * 4), ("out", C.c_int32),
+                ("iparam", C.c_int32 * 4), ("fparam", C.c_float * 2)]
+
+
 def load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -86,6 +91,16 @@ def load() -> C.CDLL:
         "hb_p2p_alloc": [vp, C.c_size_t, C.POINTER(vp), vp],
         "hb_p2p_attach": [vp, i32, i32, vp, C.c_size_t],
         "hb_all_reduce": [vp, vp, i64, i32, i32],
+        "hb_graph_create": [vp, C.POINTER(vp)],
+        "hb_graph_destroy": [vp],
+        "hb_graph_input": [vp, T, C.POINTER(i32)],
+        "hb_graph_temp": [vp, i32, i32, C.POINTER(i64), i32, C.POINTER(i32)],
+        "hb_graph_view": [vp, i32, i64, i32, C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)],
+        "hb_graph_add": [vp, C.POINTER(hb_node)],
+        "hb_graph_plan": [vp, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
+        "hb_graph_run": [vp],
+        "hb_graph_describe": [vp, C.c_char_p, C.c_size_t],
+        "hb_graph_tensor_ptr": [vp, i32, C.POINTER(vp)],
         "hb_autotune": [vp, C.POINTER(hb_op_desc), i32, C.POINTER(hb_tune_result)],
         "hb_tune_cache_load": [vp, C.c_char_p],
         "hb_tune_cache_save": [vp, C.c_char_p],

@@ -1,0 +1,409 @@
+// Model-IR executor: an ordered list of operator nodes over tensor ids, a memory planner
+// that packs planner-owned tensors into one arena by lifetime, and a launcher that walks
+// the list and enqueues every node on the context's stream (no host synchronisation
+// between nodes).
+//
+// The shape follows the one piece of the reference that walks a program: a list of
+// variant-tagged definitions visited in order and dispatched on the tag
+// (`lift_defs_exn`, tree.ml:786-811), with errors returned as values.
+//
+// Planner: a tensor lives from the first node that writes it to the last node that reads
+// it (a view extends its base).  Tensors are placed largest first at the lowest
+// 256-byte-aligned offset that does not collide, in time and space, with one already
+// placed.  Tensors flagged HB_T_SYMMETRIC (allreduce operands) go to the peer-mapped
+// buffer when the context has one that is large enough, so the collective runs over
+// NVLink without a staging copy.
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+
+#include "hb_internal.h"
+
+struct hb_graph_tensor {
+  int kind;                // 0 external, 1 planner-owned, 2 view
+  int dtype, rank;
+  int64_t shape[4], stride[4];
+  void* ptr = nullptr;     // resolved at plan time for kinds 1 and 2
+  int base = -1;           // view: tensor viewed
+  int64_t offset = 0;      // view: element offset into base
+  int flags = 0;
+  size_t bytes = 0;
+  int first = -1, last = -1;   // lifetime in node indices (owner tensors)
+  size_t arena_off = 0;
+  bool in_symmetric = false;
+};
+
+struct hb_graph {
+  hb_ctx* ctx;
+  std::vector<hb_graph_tensor> tensors;
+  std::vector<hb_node> nodes;
+  void* arena = nullptr;
+  size_t arena_bytes = 0, symmetric_bytes = 0;
+  bool planned = false;
+};
+
+namespace {
+
+const char* kNodeNames[] = {"matmul", "attention", "all_reduce", "rmsnorm", "rope", "embedding",
+                            "swiglu", "gelu", "add", "argmax"};
+size_t elem_size(int dtype) { return dtype == HB_BF16 ? 2 : 4; }
+
+int root_of(const hb_graph* g, int id) {
+  while (g->tensors[id].kind == 2) id = g->tensors[id].base;
+  return id;
+}
+
+bool valid_id(const hb_graph* g, int id) { return id >= 0 && id < (int)g->tensors.size(); }
+
+hb_tensor as_tensor(const hb_graph_tensor& t) {
+  hb_tensor o;
+  memset(&o, 0, sizeof(o));
+  o.ptr = t.ptr;
+  o.dtype = t.dtype;
+  o.rank = t.rank;
+  for (int i = 0; i < t.rank; ++i) { o.shape[i] = t.shape[i]; o.stride[i] = t.stride[i]; }
+  return o;
+}
+
+int64_t numel(const hb_graph_tensor& t) {
+  int64_t n = 1;
+  for (int i = 0; i < t.rank; ++i) n *= t.shape[i];
+  return n;
+}
+
+bool is_contiguous(const hb_graph_tensor& t) {
+  int64_t acc = 1;
+  for (int i = t.rank - 1; i >= 0; --i) {
+    if (t.shape[i] != 1 && t.stride[i] != acc) return false;
+    acc *= t.shape[i];
+  }
+  return true;
+}
+
+}  // namespace
+
+extern "C" hb_status hb_graph_create(hb_ctx* ctx, hb_graph** out) {
+  if (!ctx || !out) return HB_ERR_INVALID;
+  hb_graph* g = new hb_graph();
+  g->ctx = ctx;
+  *out = g;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_destroy(hb_graph* g) {
+  if (!g) return HB_ERR_INVALID;
+  if (g->arena) {
+    cudaSetDevice(g->ctx->device);
+    cudaStreamSynchronize(g->ctx->stream);
+    cudaFree(g->arena);
+  }
+  delete g;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_input(hb_graph* g, const hb_tensor* t, int32_t* id) {
+  if (!g || !id) return HB_ERR_INVALID;
+  if (!t || !t->ptr) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: external tensor without data");
+  if (t->rank < 1 || t->rank > 4) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: rank must be 1..4");
+  hb_graph_tensor x;
+  x.kind = 0;
+  x.dtype = t->dtype;
+  x.rank = t->rank;
+  for (int i = 0; i < 4; ++i) { x.shape[i] = i < t->rank ? t->shape[i] : 1; x.stride[i] = i < t->rank ? t->stride[i] : 0; }
+  x.ptr = t->ptr;
+  g->tensors.push_back(x);
+  *id = (int32_t)g->tensors.size() - 1;
+  g->planned = false;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_temp(hb_graph* g, int32_t dtype, int32_t rank, const int64_t* shape, int32_t flags,
+                                   int32_t* id) {
+  if (!g || !id || !shape) return HB_ERR_INVALID;
+  if (rank < 1 || rank > 4) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: rank must be 1..4");
+  if (dtype != HB_BF16 && dtype != HB_F32 && dtype != HB_I32) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: dtype %d", dtype);
+  hb_graph_tensor x;
+  x.kind = 1;
+  x.dtype = dtype;
+  x.rank = rank;
+  int64_t acc = 1;
+  for (int i = 0; i < 4; ++i) { x.shape[i] = 1; x.stride[i] = 0; }
+  for (int i = rank - 1; i >= 0; --i) {
+    if (shape[i] <= 0) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: empty dimension");
+    x.shape[i] = shape[i];
+    x.stride[i] = acc;
+    acc *= shape[i];
+  }
+  x.bytes = (size_t)acc * elem_size(dtype);
+  x.flags = flags;
+  g->tensors.push_back(x);
+  *id = (int32_t)g->tensors.size() - 1;
+  g->planned = false;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_view(hb_graph* g, int32_t base, int64_t offset, int32_t rank, const int64_t* shape,
+                                   const int64_t* stride, int32_t* id) {
+  if (!g || !id || !shape || !stride) return HB_ERR_INVALID;
+  if (!valid_id(g, base)) return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: view of unknown tensor %d", base);
+  if (rank < 1 || rank > 4 || offset < 0) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: bad view");
+  const hb_graph_tensor& b = g->tensors[base];
+  hb_graph_tensor x;
+  x.kind = 2;
+  x.dtype = b.dtype;
+  x.rank = rank;
+  int64_t extent = offset;
+  for (int i = 0; i < 4; ++i) { x.shape[i] = 1; x.stride[i] = 0; }
+  for (int i = 0; i < rank; ++i) {
+    if (shape[i] <= 0 || stride[i] < 0) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: bad view dimension");
+    x.shape[i] = shape[i];
+    x.stride[i] = stride[i];
+    extent += (shape[i] - 1) * stride[i];
+  }
+  // bounds: the view must stay inside a densely stored base
+  if (b.kind != 0 && extent >= numel(g->tensors[root_of(g, base)]) && g->tensors[root_of(g, base)].kind == 1)
+    return hb_fail(g->ctx, HB_ERR_INVALID, "graph: view reaches past the end of tensor %d", base);
+  x.base = base;
+  x.offset = offset;
+  g->tensors.push_back(x);
+  *id = (int32_t)g->tensors.size() - 1;
+  g->planned = false;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_add(hb_graph* g, const hb_node* n) {
+  if (!g || !n) return HB_ERR_INVALID;
+  if (n->kind < 0 || n->kind > HB_NODE_ARGMAX) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: unknown node kind %d", n->kind);
+  static const int n_in[] = {2, 3, 0, 2, 0, 2, 1, 1, 2, 1};   // required inputs per kind
+  for (int i = 0; i < 4; ++i) {
+    if (i < n_in[n->kind] && !valid_id(g, n->in[i]))
+      return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: %s node input %d names unknown tensor %d", kNodeNames[n->kind], i, n->in[i]);
+    if (i >= n_in[n->kind] && n->in[i] != -1 && !valid_id(g, n->in[i]))
+      return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: %s node optional input %d names unknown tensor %d", kNodeNames[n->kind], i, n->in[i]);
+  }
+  if (!valid_id(g, n->out)) return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: %s node output names unknown tensor %d", kNodeNames[n->kind], n->out);
+  g->nodes.push_back(*n);
+  g->planned = false;
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* symmetric_bytes) {
+  if (!g) return HB_ERR_INVALID;
+  hb_ctx* ctx = g->ctx;
+  // ---- lifetimes
+  for (auto& t : g->tensors) { t.first = -1; t.last = -1; }
+  auto touch = [&](int id, int node) {
+    if (id < 0) return;
+    hb_graph_tensor& r = g->tensors[root_of(g, id)];
+    if (r.first < 0) r.first = node;
+    r.last = node;
+  };
+  for (int i = 0; i < (int)g->nodes.size(); ++i) {
+    for (int k = 0; k < 4; ++k) touch(g->nodes[i].in[k], i);
+    touch(g->nodes[i].out, i);
+  }
+  // a planner-owned tensor that is read before any node wrote it would read garbage
+  for (int i = 0; i < (int)g->nodes.size(); ++i) {
+    const hb_node& n = g->nodes[i];
+    for (int k = 0; k < 4; ++k) {
+      if (n.in[k] < 0) continue;
+      const int r = root_of(g, n.in[k]);
+      if (g->tensors[r].kind != 1) continue;
+      bool written = false;
+      for (int j = 0; j < i && !written; ++j) written = root_of(g, g->nodes[j].out) == r;
+      const bool inout = (n.kind == HB_NODE_ROPE || n.kind == HB_NODE_ALL_REDUCE) && root_of(g, n.out) == r;
+      if (!written && !inout)
+        return hb_fail(ctx, HB_ERR_INVALID, "graph: node %d (%s) reads planner-owned tensor %d before any node writes it", i,
+                       kNodeNames[n.kind], n.in[k]);
+      if (!written && inout)
+        return hb_fail(ctx, HB_ERR_INVALID, "graph: node %d (%s) updates tensor %d in place before any node writes it", i,
+                       kNodeNames[n.kind], n.in[k]);
+    }
+  }
+  // ---- placement, one pass per arena (0 ordinary, 1 symmetric)
+  const bool have_sym = ctx->p2p.local != nullptr;
+  size_t totals[2] = {0, 0};
+  for (int pass = 0; pass < 2; ++pass) {
+    std::vector<int> ids;
+    for (int i = 0; i < (int)g->tensors.size(); ++i) {
+      hb_graph_tensor& t = g->tensors[i];
+      if (t.kind != 1 || t.first < 0) continue;
+      const bool sym = (t.flags & HB_T_SYMMETRIC) != 0;
+      if ((int)sym == pass) ids.push_back(i);
+    }
+    std::sort(ids.begin(), ids.end(), [&](int a, int b) {
+      if (g->tensors[a].bytes != g->tensors[b].bytes) return g->tensors[a].bytes > g->tensors[b].bytes;
+      return a < b;
+    });
+    std::vector<int> placed;
+    for (int id : ids) {
+      hb_graph_tensor& t = g->tensors[id];
+      const size_t sz = (t.bytes + 255) & ~size_t(255);
+      // candidate offsets: 0 and the end of every conflicting tensor
+      std::vector<std::pair<size_t, size_t>> busy;   // [begin, end) of time-overlapping tensors
+      for (int o : placed) {
+        const hb_graph_tensor& u = g->tensors[o];
+        if (u.last < t.first || t.last < u.first) continue;
+        busy.emplace_back(u.arena_off, u.arena_off + ((u.bytes + 255) & ~size_t(255)));
+      }
+      std::sort(busy.begin(), busy.end());
+      size_t off = 0;
+      for (const auto& b : busy) {
+        if (off + sz <= b.first) break;
+        if (b.second > off) off = b.second;
+      }
+      t.arena_off = off;
+      t.in_symmetric = pass == 1;
+      placed.push_back(id);
+      if (off + sz > totals[pass]) totals[pass] = off + sz;
+    }
+  }
+  // symmetric tensors fall back to the ordinary arena when no peer buffer can hold them
+  const bool sym_fits = have_sym && totals[1] <= ctx->p2p.bytes;
+  size_t sym_base_in_arena = 0;
+  size_t need = totals[0];
+  if (!sym_fits && totals[1] > 0) {
+    sym_base_in_arena = (totals[0] + 255) & ~size_t(255);
+    need = sym_base_in_arena + totals[1];
+  }
+  if (need > g->arena_bytes) {
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaSetDevice");
+    if (g->arena) { cudaStreamSynchronize(ctx->stream); cudaFree(g->arena); g->arena = nullptr; g->arena_bytes = 0; }
+    e = cudaMalloc(&g->arena, need);
+    if (e != cudaSuccess) { cudaGetLastError(); return hb_fail(ctx, HB_ERR_NOMEM, "graph: cannot allocate a %zu-byte arena", need); }
+    g->arena_bytes = need;
+  }
+  for (auto& t : g->tensors) {
+    if (t.kind != 1 || t.first < 0) continue;
+    if (t.in_symmetric && sym_fits) t.ptr = static_cast<char*>(ctx->p2p.local) + t.arena_off;
+    else if (t.in_symmetric) { t.ptr = static_cast<char*>(g->arena) + sym_base_in_arena + t.arena_off; }
+    else t.ptr = static_cast<char*>(g->arena) + t.arena_off;
+  }
+  for (auto& t : g->tensors) {
+    if (t.kind != 2) continue;
+    // resolve view chains: pointer = root pointer + accumulated element offsets
+    int64_t off = 0;
+    int id = (int)(&t - &g->tensors[0]);
+    while (g->tensors[id].kind == 2) { off += g->tensors[id].offset; id = g->tensors[id].base; }
+    const hb_graph_tensor& r = g->tensors[id];
+    t.ptr = r.ptr ? static_cast<char*>(r.ptr) + off * (int64_t)elem_size(r.dtype) : nullptr;
+  }
+  g->symmetric_bytes = totals[1];
+  g->planned = true;
+  if (arena_bytes) *arena_bytes = need;
+  if (symmetric_bytes) *symmetric_bytes = totals[1];
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_run(hb_graph* g) {
+  if (!g) return HB_ERR_INVALID;
+  hb_ctx* ctx = g->ctx;
+  if (!g->planned) return hb_fail(ctx, HB_ERR_INVALID, "graph: call hb_graph_plan before hb_graph_run");
+  for (int i = 0; i < (int)g->nodes.size(); ++i) {
+    const hb_node& n = g->nodes[i];
+    auto T = [&](int id) -> const hb_graph_tensor& { return g->tensors[id]; };
+    hb_status st = HB_OK;
+    switch (n.kind) {
+      case HB_NODE_MATMUL: {
+        hb_tensor a = as_tensor(T(n.in[0])), b = as_tensor(T(n.in[1])), c = as_tensor(T(n.out));
+        hb_matmul_opts o = {n.iparam[0], n.iparam[1], nullptr, 0};
+        if (n.iparam[0] == HB_EPI_RESIDUAL) {
+          if (n.in[2] < 0) { st = hb_fail(ctx, HB_ERR_INVALID, "graph: residual epilogue without a residual tensor"); break; }
+          o.residual = T(n.in[2]).ptr;
+          o.residual_ld = T(n.in[2]).stride[0];
+        }
+        st = hb_matmul(ctx, &a, &b, &c, &o);
+        break;
+      }
+      case HB_NODE_ATTENTION: {
+        hb_tensor q = as_tensor(T(n.in[0])), k = as_tensor(T(n.in[1])), v = as_tensor(T(n.in[2])), o = as_tensor(T(n.out));
+        hb_attn_opts opts = {n.iparam[0], n.fparam[0], n.in[3] >= 0 ? T(n.in[3]).ptr : nullptr, -1};
+        st = hb_attention(ctx, &q, &k, &v, &o, &opts);
+        break;
+      }
+      case HB_NODE_ALL_REDUCE: {
+        const hb_graph_tensor& x = T(n.out);
+        if (!is_contiguous(x)) { st = hb_fail(ctx, HB_ERR_UNSUPPORTED, "graph: all_reduce needs a contiguous tensor"); break; }
+        st = hb_all_reduce(ctx, x.ptr, numel(x), x.dtype, n.iparam[0]);
+        break;
+      }
+      case HB_NODE_RMSNORM: {
+        const hb_graph_tensor& x = T(n.in[0]);
+        if (x.rank != 2 || !is_contiguous(x) || !is_contiguous(T(n.out))) { st = hb_fail(ctx, HB_ERR_UNSUPPORTED, "graph: rmsnorm needs contiguous [rows, cols]"); break; }
+        st = hb_rmsnorm(ctx, x.ptr, T(n.in[1]).ptr, T(n.out).ptr, n.in[2] >= 0 ? T(n.in[2]).ptr : nullptr, x.shape[0], x.shape[1],
+                        n.fparam[0]);
+        break;
+      }
+      case HB_NODE_ROPE: {
+        const hb_graph_tensor& x = T(n.out);   // [tokens, heads * head_dim] with a row stride
+        if (x.rank != 2 || x.stride[1] != 1) { st = hb_fail(ctx, HB_ERR_UNSUPPORTED, "graph: rope needs [tokens, heads*head_dim] rows"); break; }
+        st = hb_rope(ctx, x.ptr, x.shape[0], n.iparam[0], n.iparam[1], n.iparam[2], x.stride[0], n.fparam[0], n.iparam[3]);
+        break;
+      }
+      case HB_NODE_EMBEDDING: {
+        const hb_graph_tensor& tab = T(n.in[0]);
+        st = hb_embedding(ctx, tab.ptr, static_cast<const int32_t*>(T(n.in[1]).ptr), T(n.out).ptr, T(n.in[1]).shape[0],
+                          tab.shape[0], tab.shape[1]);
+        break;
+      }
+      case HB_NODE_SWIGLU: {
+        const hb_graph_tensor& x = T(n.in[0]);
+        st = hb_swiglu(ctx, x.ptr, T(n.out).ptr, x.shape[0], x.shape[1] / 2);
+        break;
+      }
+      case HB_NODE_GELU:
+        st = hb_gelu(ctx, T(n.in[0]).ptr, T(n.out).ptr, numel(T(n.in[0])));
+        break;
+      case HB_NODE_ADD:
+        st = hb_add(ctx, T(n.in[0]).ptr, T(n.in[1]).ptr, T(n.out).ptr, numel(T(n.in[0])));
+        break;
+      case HB_NODE_ARGMAX: {
+        const hb_graph_tensor& x = T(n.in[0]);
+        st = hb_argmax(ctx, x.ptr, static_cast<int32_t*>(T(n.out).ptr), x.shape[0], x.shape[1]);
+        break;
+      }
+      default:
+        st = hb_fail(ctx, HB_ERR_INVALID, "graph: unknown node kind %d", n.kind);
+    }
+    if (st != HB_OK) {
+      std::string inner = ctx->err;
+      return hb_fail(ctx, st, "graph node %d (%s): %s", i, kNodeNames[n.kind], inner.c_str());
+    }
+  }
+  return HB_OK;
+}
+
+// Text listing of the planned graph: one line per node, then one per planner-owned
+// tensor with its lifetime and arena offset.
+extern "C" hb_status hb_graph_describe(hb_graph* g, char* buf, size_t len) {
+  if (!g || !buf || len == 0) return HB_ERR_INVALID;
+  std::string s;
+  char line[256];
+  for (int i = 0; i < (int)g->nodes.size(); ++i) {
+    const hb_node& n = g->nodes[i];
+    snprintf(line, sizeof(line), "n%d %s in(%d,%d,%d,%d) out %d\n", i, kNodeNames[n.kind], n.in[0], n.in[1], n.in[2], n.in[3], n.out);
+    s += line;
+  }
+  for (int i = 0; i < (int)g->tensors.size(); ++i) {
+    const hb_graph_tensor& t = g->tensors[i];
+    if (t.kind != 1) continue;
+    snprintf(line, sizeof(line), "t%d %s bytes %zu live [%d,%d] %s+%zu\n", i, t.dtype == HB_BF16 ? "bf16" : t.dtype == HB_F32 ? "f32" : "i32",
+             t.bytes, t.first, t.last, t.in_symmetric ? "sym" : "arena", t.arena_off);
+    s += line;
+  }
+  snprintf(line, sizeof(line), "arena %zu symmetric %zu\n", g->arena_bytes, g->symmetric_bytes);
+  s += line;
+  if (s.size() + 1 > len) return hb_fail(g->ctx, HB_ERR_NOMEM, "graph: describe needs %zu bytes", s.size() + 1);
+  memcpy(buf, s.c_str(), s.size() + 1);
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_tensor_ptr(hb_graph* g, int32_t id, void** ptr) {
+  if (!g || !ptr) return HB_ERR_INVALID;
+  if (!valid_id(g, id)) return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: unknown tensor %d", id);
+  if (!g->planned) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: not planned");
+  *ptr = g->tensors[id].ptr;
+  return HB_OK;
+}

@@ -1,0 +1,114 @@
+"""Host-side wrapper of the model-IR executor (``hb_graph_*`` in the C ABI): build an
+ordered node list over tensor ids, let the library plan the arena, and run it."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+from . import _capi
+from .model_ir import Context, Tensor, _contig, _lib
+
+(NODE_MATMUL, NODE_ATTENTION, NODE_ALL_REDUCE, NODE_RMSNORM, NODE_ROPE, NODE_EMBEDDING, NODE_SWIGLU, NODE_GELU,
+ NODE_ADD, NODE_ARGMAX) = range(10)
+T_SYMMETRIC = 1
+
+
+class Graph:
+    def __init__(self, ctx: Context):
+        self.ctx = ctx
+        h = C.c_void_p()
+        ctx._check(_lib.hb_graph_create(ctx._h, C.byref(h)))
+        self._h = h
+        self.meta = {}          # id -> (dtype, shape, stride)
+
+    def close(self):
+        if self._h:
+            _lib.hb_graph_destroy(self._h)
+            self._h = None
+
+    # -- tensors ------------------------------------------------------------------
+    def input(self, t: Tensor) -> int:
+        i = C.c_int32()
+        ct = t.c()
+        self.ctx._check(_lib.hb_graph_input(self._h, C.byref(ct), C.byref(i)))
+        self.meta[i.value] = (t.dtype, tuple(t.shape), tuple(t.stride))
+        return i.value
+
+    def temp(self, shape: Sequence[int], dtype: int = _capi.HB_BF16, symmetric: bool = False) -> int:
+        i = C.c_int32()
+        arr = (C.c_int64 * len(shape))(*shape)
+        self.ctx._check(_lib.hb_graph_temp(self._h, dtype, len(shape), arr, T_SYMMETRIC if symmetric else 0, C.byref(i)))
+        self.meta[i.value] = (dtype, tuple(shape), _contig(tuple(shape)))
+        return i.value
+
+    def view(self, base: int, offset: int, shape: Sequence[int], stride: Sequence[int]) -> int:
+        i = C.c_int32()
+        self.ctx._check(_lib.hb_graph_view(self._h, base, offset, len(shape), (C.c_int64 * len(shape))(*shape),
+                                           (C.c_int64 * len(stride))(*stride), C.byref(i)))
+        self.meta[i.value] = (self.meta[base][0], tuple(shape), tuple(stride))
+        return i.value
+
+    # -- nodes --------------------------------------------------------------------
+    def _add(self, kind, ins, out, iparam=(), fparam=()):
+        n = _capi.hb_node()
+        n.kind = kind
+        for k in range(4):
+            n.inputs[k] = ins[k] if k < len(ins) and ins[k] is not None else -1
+            n.iparam[k] = iparam[k] if k < len(iparam) else 0
+        n.out = out
+        for k in range(2):
+            n.fparam[k] = fparam[k] if k < len(fparam) else 0.0
+        self.ctx._check(_lib.hb_graph_add(self._h, C.byref(n)))
+        return out
+
+    def matmul(self, a, b, out, epilogue=_capi.HB_EPI_NONE, residual=None, config_id=-1):
+        return self._add(NODE_MATMUL, [a, b, residual], out, [epilogue, config_id])
+
+    def attention(self, q, k, v, out, causal=True, scale=None, lse=None):
+        if scale is None:
+            scale = float(self.meta[q][1][-1]) ** -0.5
+        return self._add(NODE_ATTENTION, [q, k, v, lse], out, [int(causal)], [scale])
+
+    def all_reduce(self, x, algo=_capi.HB_AR_AUTO):
+        return self._add(NODE_ALL_REDUCE, [], x, [algo])
+
+    def rmsnorm(self, x, gain, out, residual=None, eps=1e-5):
+        return self._add(NODE_RMSNORM, [x, gain, residual], out, [], [eps])
+
+    def rope(self, x, seq, heads, head_dim, base=10000.0, pos0=0):
+        return self._add(NODE_ROPE, [], x, [seq, heads, head_dim, pos0], [base])
+
+    def embedding(self, table, ids, out):
+        return self._add(NODE_EMBEDDING, [table, ids], out)
+
+    def swiglu(self, x, out):
+        return self._add(NODE_SWIGLU, [x], out)
+
+    def gelu(self, x, out):
+        return self._add(NODE_GELU, [x], out)
+
+    def add(self, a, b, out):
+        return self._add(NODE_ADD, [a, b], out)
+
+    def argmax(self, x, out):
+        return self._add(NODE_ARGMAX, [x], out)
+
+    # -- plan / run -----------------------------------------------------------------
+    def plan(self):
+        a, s = C.c_size_t(), C.c_size_t()
+        self.ctx._check(_lib.hb_graph_plan(self._h, C.byref(a), C.byref(s)))
+        return a.value, s.value
+
+    def run(self):
+        self.ctx._check(_lib.hb_graph_run(self._h))
+
+    def describe(self) -> str:
+        buf = C.create_string_buffer(1 << 16)
+        self.ctx._check(_lib.hb_graph_describe(self._h, buf, len(buf)))
+        return buf.value.decode()
+
+    def tensor(self, i: int) -> Tensor:
+        p = C.c_void_p()
+        self.ctx._check(_lib.hb_graph_tensor_ptr(self._h, i, C.byref(p)))
+        dtype, shape, stride = self.meta[i]
+        return Tensor(p.value, dtype, shape, stride)

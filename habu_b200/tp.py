@@ -1,0 +1,149 @@
+"""Megatron-style tensor-parallel decoder block on the model-IR executor.
+
+Sharding (rank r of n): query heads and KV heads are split by head, so grouped-query
+groups stay rank-local; the QKV and gate/up projections are column-parallel, the
+attention-out and FFN-down projections row-parallel, each followed by one sum-allreduce
+of the [tokens, d_model] partial result.  RMSNorm, RoPE and the residual stream are
+replicated.  Weights are stored the way the matmul node wants a column-major B: one
+row per output feature, K contiguous.
+
+Pure index arithmetic lives in the ``shard_*`` functions (no GPU needed); ``DecoderGraph``
+builds the node list for one rank.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List
+
+import numpy as np
+
+from . import _capi
+
+
+@dataclass(frozen=True)
+class DecoderConfig:
+    d_model: int = 4096
+    n_q_heads: int = 32
+    n_kv_heads: int = 8
+    head_dim: int = 128
+    ffn_hidden: int = 14336
+    n_layers: int = 2
+    batch: int = 4
+    seq: int = 2048
+    eps: float = 1e-5
+    rope_base: float = 10000.0
+
+    @property
+    def tokens(self) -> int:
+        return self.batch * self.seq
+
+    def flops(self) -> float:
+        """Algorithmic flop of one forward (GEMMs + causal attention by the usual count)."""
+        T, d, hd = self.tokens, self.d_model, self.head_dim
+        qkv = 2.0 * T * d * (self.n_q_heads + 2 * self.n_kv_heads) * hd
+        attn = 4.0 * self.batch * self.n_q_heads * self.seq * self.seq * hd / 2
+        out = 2.0 * T * self.n_q_heads * hd * d
+        ffn = 2.0 * T * d * 2 * self.ffn_hidden + 2.0 * T * self.ffn_hidden * d
+        return self.n_layers * (qkv + attn + out + ffn)
+
+
+def shard_range(total: int, world: int, rank: int):
+    if total % world:
+        raise ValueError(f"{total} does not split over {world} ranks")
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+def check_shardable(cfg: DecoderConfig, world: int):
+    if cfg.n_q_heads % cfg.n_kv_heads:
+        raise ValueError("query heads must be a multiple of KV heads")
+    for name, v in (("n_kv_heads", cfg.n_kv_heads), ("n_q_heads", cfg.n_q_heads), ("ffn_hidden", cfg.ffn_hidden)):
+        if v % world:
+            raise ValueError(f"{name}={v} does not split over {world} ranks")
+    if (cfg.ffn_hidden // world) % 8:
+        raise ValueError("local FFN width must be a multiple of 8")
+
+
+def shard_layer(full: Dict[str, np.ndarray], cfg: DecoderConfig, world: int, rank: int) -> Dict[str, np.ndarray]:
+    """Slice one layer's full weights ([out_features, in_features] each) for `rank`.
+
+    full: wq [Hq*hd, d], wk/wv [Hkv*hd, d], wo [d, Hq*hd], wg/wu [F, d], wd [d, F], g1/g2 [d].
+    Returns wqkv [(q+2kv)_local*hd, d], wo [d, q_local*hd], wgu [2*F_local, d] with rows
+    interleaved (gate_j, up_j), wd [d, F_local], and the replicated gains.
+    """
+    check_shardable(cfg, world)
+    hd = cfg.head_dim
+    q0, q1 = shard_range(cfg.n_q_heads, world, rank)
+    k0, k1 = shard_range(cfg.n_kv_heads, world, rank)
+    f0, f1 = shard_range(cfg.ffn_hidden, world, rank)
+    wqkv = np.concatenate([full["wq"][q0 * hd:q1 * hd], full["wk"][k0 * hd:k1 * hd], full["wv"][k0 * hd:k1 * hd]], 0)
+    wgu = np.empty((2 * (f1 - f0), cfg.d_model), full["wg"].dtype)
+    wgu[0::2] = full["wg"][f0:f1]
+    wgu[1::2] = full["wu"][f0:f1]
+    return {"wqkv": np.ascontiguousarray(wqkv), "wo": np.ascontiguousarray(full["wo"][:, q0 * hd:q1 * hd]),
+            "wgu": wgu, "wd": np.ascontiguousarray(full["wd"][:, f0:f1]), "g1": full["g1"], "g2": full["g2"]}
+
+
+class DecoderGraph:
+    """Node list of the decoder forward for one rank; weights are bf16 bit patterns."""
+
+    def __init__(self, ctx, cfg: DecoderConfig, world: int, rank: int, layers: List[Dict[str, np.ndarray]],
+                 algo: int = _capi.HB_AR_AUTO):
+        from .graph import Graph
+        check_shardable(cfg, world)
+        self.ctx, self.cfg, self.world, self.rank = ctx, cfg, world, rank
+        T, d, hd = cfg.tokens, cfg.d_model, cfg.head_dim
+        ql, kl, fl = cfg.n_q_heads // world, cfg.n_kv_heads // world, cfg.ffn_hidden // world
+        W = (ql + 2 * kl) * hd
+        g = self.graph = Graph(ctx)
+        self.x0 = ctx.empty((T, d))
+        self.out = ctx.empty((T, d))
+        x0, out = g.input(self.x0), g.input(self.out)
+        self.weights = []
+        x = None                       # residual stream (planner-owned after the first add)
+        pending = None                 # sublayer output not yet added into the stream
+        for li, lw in enumerate(layers):
+            dev = {k: ctx.upload(v) for k, v in lw.items()}
+            self.weights.append(dev)
+            w = {k: g.input(v if k in ("g1", "g2") else v.T) for k, v in dev.items()}
+            # ---- attention sublayer
+            h = g.temp((T, d))
+            if x is None:
+                g.rmsnorm(x0, w["g1"], h, eps=cfg.eps)
+            else:
+                g.rmsnorm(pending, w["g1"], h, residual=x, eps=cfg.eps)
+            qkv = g.temp((T, W))
+            g.matmul(h, w["wqkv"], qkv)
+            g.rope(g.view(qkv, 0, (T, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
+            g.rope(g.view(qkv, ql * hd, (T, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
+            v4 = lambda off, H: g.view(qkv, off, (cfg.batch, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
+            attn = g.temp((T, ql * hd))
+            g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
+                        g.view(attn, 0, (cfg.batch, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)), causal=True)
+            ao = g.temp((T, d), symmetric=True)
+            g.matmul(attn, w["wo"], ao)
+            g.all_reduce(ao, algo)
+            # ---- FFN sublayer
+            h2 = g.temp((T, d))
+            if x is None:
+                x = g.temp((T, d))
+                g.add(x0, ao, x)
+                g.rmsnorm(x, w["g2"], h2, eps=cfg.eps)
+            else:
+                g.rmsnorm(ao, w["g2"], h2, residual=x, eps=cfg.eps)
+            act = g.temp((T, fl))
+            g.matmul(h2, w["wgu"], act, epilogue=_capi.HB_EPI_SWIGLU)
+            fo = g.temp((T, d), symmetric=True)
+            g.matmul(act, w["wd"], fo)
+            g.all_reduce(fo, algo)
+            pending = fo
+        g.add(x, pending, out)
+        self.symmetric_needed = None
+
+    def plan(self):
+        arena, sym = self.graph.plan()
+        self.symmetric_needed = sym
+        return arena, sym
+
+    def run(self):
+        self.graph.run()

@@ -159,6 +159,50 @@ hb_status hb_p2p_attach(hb_ctx* ctx, int32_t world, int32_t rank, const void* al
                         size_t bytes);
 hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo);
 
+/* ---- model-IR executor: node list, memory planner, launcher --------------------------
+ * A graph is an ordered list of operator nodes over tensor ids.  `hb_graph_plan` computes
+ * each planner-owned tensor's lifetime and packs them into one arena (and the tensors
+ * flagged HB_T_SYMMETRIC into the peer-mapped buffer, when the context has one, so that
+ * allreduce runs in place over NVLink); `hb_graph_run` enqueues every node on the
+ * context's stream.  Shape taken from the reference's only program walker, a list of
+ * variant-tagged definitions dispatched in order (`lift_defs_exn`, tree.ml:786-811). */
+typedef struct hb_graph hb_graph;
+enum {
+  HB_NODE_MATMUL = 0,      /* in: A, B, [residual]      iparam: epilogue, config_id          */
+  HB_NODE_ATTENTION = 1,   /* in: Q, K, V, [lse]        iparam: causal        fparam: scale   */
+  HB_NODE_ALL_REDUCE = 2,  /* in place on `out`         iparam: algorithm                     */
+  HB_NODE_RMSNORM = 3,     /* in: x, gain, [residual]                         fparam: eps     */
+  HB_NODE_ROPE = 4,        /* in place on `out`         iparam: seq, heads, head_dim, pos0; fparam: base */
+  HB_NODE_EMBEDDING = 5,   /* in: table, ids */
+  HB_NODE_SWIGLU = 6,      /* in: x */
+  HB_NODE_GELU = 7,        /* in: x */
+  HB_NODE_ADD = 8,         /* in: a, b */
+  HB_NODE_ARGMAX = 9       /* in: x */
+};
+enum { HB_T_SYMMETRIC = 1 };
+typedef struct hb_node {
+  int32_t kind;
+  int32_t in[4];           /* tensor ids, -1 where unused */
+  int32_t out;
+  int32_t iparam[4];
+  float fparam[2];
+} hb_node;
+hb_status hb_graph_create(hb_ctx* ctx, hb_graph** out);
+hb_status hb_graph_destroy(hb_graph* g);
+/* Caller-owned tensor (weights, inputs, outputs). */
+hb_status hb_graph_input(hb_graph* g, const hb_tensor* t, int32_t* id);
+/* Planner-owned contiguous tensor. */
+hb_status hb_graph_temp(hb_graph* g, int32_t dtype, int32_t rank, const int64_t* shape,
+                        int32_t flags, int32_t* id);
+/* View of another tensor: element offset, shape and strides (elements). */
+hb_status hb_graph_view(hb_graph* g, int32_t base, int64_t offset, int32_t rank,
+                        const int64_t* shape, const int64_t* stride, int32_t* id);
+hb_status hb_graph_add(hb_graph* g, const hb_node* node);
+hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* symmetric_bytes);
+hb_status hb_graph_run(hb_graph* g);
+hb_status hb_graph_describe(hb_graph* g, char* buf, size_t len);
+hb_status hb_graph_tensor_ptr(hb_graph* g, int32_t id, void** ptr);
+
 /* ---- autotune entry point ----------------------------------------------------------
  * Searches tile shape / cluster shape / stage count / raster order for one problem
  * shape by timing each candidate on the device, records the winner in the context's

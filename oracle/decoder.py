@@ -1,0 +1,62 @@
+"""CPU restatement of the Llama-style decoder block forward (test infrastructure only).
+
+No reference implementation exists (parity unpinned); this follows the configuration's
+definition: pre-norm blocks, RMSNorm eps 1e-5 with gain, rotate-half RoPE base 10000,
+grouped-query causal attention with scale 1/sqrt(head_dim), SwiGLU FFN, residual adds.
+``round_bf16=True`` rounds every tensor the device stores in bf16 at the same points
+(the "bf16-storage" mode); ``False`` keeps fp32 throughout (the fp32 reference).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+import oracle
+
+SEED = 0x48414255
+
+
+def make_layer(cfg, layer: int, seed: int = SEED):
+    """Full (unsharded) weights of one layer, N(0, 0.02) rounded to bf16, gains = 1.
+    Each matrix is [out_features, in_features]."""
+    d, hd = cfg.d_model, cfg.head_dim
+    s = seed + 100 * (layer + 1)
+    mk = lambda shape, k: oracle.round_bf16(oracle.normal(shape, s + k, 0.0, 0.02))
+    return {"wq": mk((cfg.n_q_heads * hd, d), 1), "wk": mk((cfg.n_kv_heads * hd, d), 2),
+            "wv": mk((cfg.n_kv_heads * hd, d), 3), "wo": mk((d, cfg.n_q_heads * hd), 4),
+            "wg": mk((cfg.ffn_hidden, d), 5), "wu": mk((cfg.ffn_hidden, d), 6), "wd": mk((d, cfg.ffn_hidden), 7),
+            "g1": np.ones(d, np.float32), "g2": np.ones(d, np.float32)}
+
+
+def make_input(cfg, seed: int = SEED):
+    return oracle.round_bf16(oracle.normal((cfg.tokens, cfg.d_model), seed + 7))
+
+
+def forward(cfg, x0, layers, round_bf16=True, heads=None, ffn=None, reduce=None):
+    """Decoder forward.  `heads=(q0,q1,k0,k1)` and `ffn=(f0,f1)` restrict the computation
+    to one rank's shard, in which case `reduce` (a function summing partials across
+    ranks) must be given; with all three None the whole model is evaluated."""
+    rnd = (lambda a: oracle.round_bf16(np.ascontiguousarray(a, np.float32))) if round_bf16 else (lambda a: np.ascontiguousarray(a, np.float32))
+    hd, B, S = cfg.head_dim, cfg.batch, cfg.seq
+    q0, q1, k0, k1 = heads if heads else (0, cfg.n_q_heads, 0, cfg.n_kv_heads)
+    f0, f1 = ffn if ffn else (0, cfg.ffn_hidden)
+    reduce = reduce or (lambda a: a)
+    x = x0.astype(np.float32)
+    for lw in layers:
+        h = rnd(oracle.rmsnorm(x, lw["g1"], cfg.eps))
+        q = rnd(oracle.gemm(h, lw["wq"][q0 * hd:q1 * hd].T))
+        k = rnd(oracle.gemm(h, lw["wk"][k0 * hd:k1 * hd].T))
+        v = rnd(oracle.gemm(h, lw["wv"][k0 * hd:k1 * hd].T))
+        q = rnd(oracle.rope(q, S, q1 - q0, hd, cfg.rope_base))
+        k = rnd(oracle.rope(k, S, k1 - k0, hd, cfg.rope_base))
+        a = oracle.attention(q.reshape(B, S, q1 - q0, hd), k.reshape(B, S, k1 - k0, hd), v.reshape(B, S, k1 - k0, hd),
+                             causal=True, round_p=round_bf16)
+        a = rnd(a.reshape(B * S, (q1 - q0) * hd))
+        ao = reduce(rnd(oracle.gemm(a, np.ascontiguousarray(lw["wo"][:, q0 * hd:q1 * hd]).T)))
+        x = rnd(x + rnd(ao))
+        h2 = rnd(oracle.rmsnorm(x, lw["g2"], cfg.eps))
+        g = oracle.gemm(h2, lw["wg"][f0:f1].T)
+        u = oracle.gemm(h2, lw["wu"][f0:f1].T)
+        act = rnd(oracle.swiglu(np.concatenate([g, u], 1)))
+        fo = reduce(rnd(oracle.gemm(act, np.ascontiguousarray(lw["wd"][:, f0:f1]).T)))
+        x = rnd(x + rnd(fo))
+    return x
