@@ -199,8 +199,93 @@ class AttentionWorkload:
                 f"{heads} of {self.B * self.H} (batch, head) pairs at seq {self.S} (oracle attention, fp32)")
 
 
+class DecoderWorkload:
+    """Llama-style decoder block forward x2 layers, bf16, tensor-parallel over all ranks:
+    d_model 4096, 32 query / 8 KV heads, head_dim 128, SwiGLU hidden 14336, batch 4 x seq 2048."""
+    bound = "tensor"
+    kernel = "hb_gemm_bf16_kernel"
+    flush = None
+    scaling = "strong"
+
+    def __init__(self, name="decoder"):
+        from habu_b200.tp import DecoderConfig
+        self.name, self.cfg = name, DecoderConfig()
+        self.flop = self.cfg.flops()
+        self.tokens = self.cfg.tokens
+        self.metric, self.unit = "decoder_tokens_per_s", "tokens/s"
+        self.desc = ("Llama-style decoder block forward x2 layers bf16: d_model 4096, 32 q / 8 kv heads, head_dim 128, "
+                     "SwiGLU 14336, RMSNorm eps 1e-5, RoPE base 10000, batch 4 x seq 2048, weights N(0,0.02), "
+                     "embeddings N(0,1); Megatron tensor parallel, allreduce after attention-out and FFN-down")
+        self.flush_note = "weights + activations per step exceed L2 (weights alone 872 MB / TP)"
+
+    def setup(self, ctx, rank, pinned, world=1, dist=None):
+        import oracle
+        from habu_b200 import HB_AR_AUTO
+        from habu_b200.tp import DecoderGraph, shard_layer
+        from oracle import decoder
+        cfg = self.cfg
+        layers = []
+        for i in range(cfg.n_layers):
+            full = decoder.make_layer(cfg, i)
+            layers.append({k: oracle.to_bf16_bits(v) for k, v in shard_layer(full, cfg, world, rank).items()})
+            del full
+        self.dg = DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO)
+        _, sym = self.dg.plan()
+        if world > 1:
+            ids = [ctx.comm_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            ctx.comm_init_rank(world, rank, ids[0])
+            _, handle = ctx.p2p_alloc(sym)
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            ctx.p2p_attach(world, rank, handles, sym)
+            self.dg.plan()
+        x0 = oracle.to_bf16_bits(decoder.make_input(cfg))
+        self.hX = pinned(x0)
+        self.hO = pinned(np.empty_like(x0))
+        self._copy(ctx, self.dg.x0.ptr, self.hX, up=True)
+        ctx.sync()
+        self.h2d, self.d2h = x0.nbytes, x0.nbytes
+        self.world = world
+
+    @staticmethod
+    def _copy(ctx, dev_ptr, host, up):
+        import ctypes as C
+        from habu_b200 import model_ir
+        f = model_ir._lib.hb_upload if up else model_ir._lib.hb_download
+        a, b = (C.c_void_p(dev_ptr), host.ctypes.data_as(C.c_void_p))
+        ctx._check(f(ctx._h, a, b, host.nbytes) if up else f(ctx._h, b, a, host.nbytes))
+
+    def step(self, ctx):
+        self.dg.run()
+
+    def step_e2e(self, ctx):
+        self._copy(ctx, self.dg.x0.ptr, self.hX, up=True)
+        self.dg.run()
+        self._copy(ctx, self.dg.out.ptr, self.hO, up=False)
+        ctx.sync()
+
+    def value(self, ms, world):
+        return self.tokens / (ms * 1e-3)
+
+    def cpu_sample(self, max_rows=None):
+        """Bounded CPU sample: the same block at batch 1 x seq 256 on the oracle (fp32)."""
+        from dataclasses import replace
+        from oracle import decoder
+        cfg = replace(self.cfg, batch=1, seq=256 if max_rows is None else 128, n_layers=1)
+        layers = [decoder.make_layer(cfg, 0)]
+        x0 = decoder.make_input(cfg)
+        t0 = time.perf_counter()
+        decoder.forward(cfg, x0, layers, round_bf16=False)
+        dt = time.perf_counter() - t0
+        return cfg.tokens / dt * (1.0 / self.cfg.n_layers), (
+            f"1 of {self.cfg.n_layers} layers at batch 1 x seq {cfg.seq} (oracle decoder, fp32), scaled to tokens/s of "
+            f"the {self.cfg.n_layers}-layer block")
+
+
 WORKLOADS = {
     "attention": lambda: AttentionWorkload("attention", 8, 4096, 32),
+    "decoder": lambda: DecoderWorkload(),
     "gemm": lambda: GemmWorkload("gemm", 8192, 8192, 8192),
     "gemm4096": lambda: GemmWorkload("gemm4096", 4096, 4096, 4096),
     "gemm1024": lambda: GemmWorkload("gemm1024", 1024, 1024, 1024),
@@ -223,7 +308,7 @@ def run_reference(args, rank, world):
     v = float(np.mean(vals))
     line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl.desc},
             "cpu_baseline": {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
                              "sample": sample + "; the reference project has no implementation of this path"},
@@ -237,6 +322,8 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="gemm", choices=sorted(WORKLOADS))
+    ap.add_argument("--extras", default="attention,decoder",
+                    help="comma-separated workloads also measured (device-resident leg only) and reported under 'extras'")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -257,9 +344,8 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    ctx = hb.Context(local_rank)
     stream = torch.cuda.Stream()
-    ctx.set_stream(stream.cuda_stream)
+    pk = peaks()
 
     def pinned(a: np.ndarray) -> np.ndarray:
         t = torch.empty(a.shape, dtype={2: torch.int16, 4: torch.float32}[a.dtype.itemsize]).pin_memory()
@@ -269,90 +355,115 @@ def main():
         return out
     pinned.keep = []
 
-    wl = WORKLOADS[args.workload]()
-    wl.setup(ctx, rank, pinned)
+    def measure(name, steps, warmup, full):
+        """Times one workload.  full=False: device-resident leg only."""
+        ctx = hb.Context(local_rank)
+        ctx.set_stream(stream.cuda_stream)
+        wl = WORKLOADS[name]()
+        sharded = getattr(wl, "scaling", "weak") == "strong"
+        if sharded:
+            wl.setup(ctx, rank, pinned, world, dist)
+        else:
+            wl.setup(ctx, rank, pinned)
 
-    def barrier():
-        ctx.sync()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+        def barrier():
+            ctx.sync()
             torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+                torch.cuda.synchronize()
 
-    def timed(fn, steps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        def timed(fn, n):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            e0.record(stream)
+            for _ in range(n):
+                fn(ctx)
+            e1.record(stream)
+            barrier()
+            ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            return float(ms.item())
+
+        for _ in range(warmup):
+            wl.step(ctx)
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        l0 = ctx.launches
+        total_ms = timed(wl.step, steps)
+        launches = ctx.launches - l0
+        clocks = sampler.stop() if rank == 0 else None
+        ms_per_step = total_ms / steps
+        kern_ms = ms_per_step
+        if wl.flush is not None:
+            # the flush kernel's own time, measured the same way, is taken out of the step
+            flush_ms = timed(lambda c: c.add(wl.flush, wl.flush, wl.flush), steps) / steps
+            kern_ms = max(ms_per_step - flush_ms, 1e-6)
+        if sharded:
+            value = wl.value(kern_ms, world)
+            achieved = wl.flop / world / (kern_ms * 1e-3) / 1e12       # per-GPU share of the algorithmic work
+        else:
+            value = wl.flop * world / (kern_ms * 1e-3) / 1e12
+            achieved = wl.flop / (kern_ms * 1e-3) / 1e12
+        long_run = total_ms > 1000.0
+        if wl.bound == "tensor":
+            peak = pk["bf16_sustained"] if long_run else pk["bf16_burst"]
+            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_kind": ("sustained" if long_run else "burst") + " cuBLAS bf16, of " + pk["source"]}
+        else:
+            achieved = wl.bytes / (kern_ms * 1e-3) / 1e9
+            roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm"], "peak_kind": "STREAM-style copy, of " + pk["source"]}
+        roof["traffic"] = NCU_TRAFFIC_BYTES.get(wl.name)
+        roof["kernel"] = wl.kernel
+        roof["kernel_ms"] = kern_ms
+        if sharded:
+            roof["note"] = "whole-step figure: algorithmic flop of the block / (n_gpus x step time), all kernels and collectives included"
+        res = {"metric": wl.metric, "value": value, "unit": wl.unit, "ms_per_step": ms_per_step, "steps": steps,
+               "scaling": getattr(wl, "scaling", "weak"), "workload": wl.desc, "l2": wl.flush_note, "roofline": roof,
+               "gpu_launches": launches, "clocks": clocks}
+        if full:
+            e2e_steps = max(3, min(steps, 10))
+            wl.step_e2e(ctx)
+            e2e_ms = timed(wl.step_e2e, e2e_steps) / e2e_steps
+            e2e_value = wl.value(e2e_ms, world) if sharded else wl.flop * world / (e2e_ms * 1e-3) / 1e12
+            res["e2e"] = {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
+                          "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms}
+            if world == 1 and rank == 0 and not args.no_cpu_baseline:
+                import oracle
+                v, sample = wl.cpu_sample()
+                res["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
+                                       "sample": sample}
         barrier()
-        e0.record(stream)
-        for _ in range(steps):
-            fn(ctx)
-        e1.record(stream)
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        ctx.close()
+        pinned.keep.clear()
+        return res
 
-    # ---- device-resident leg
-    for _ in range(args.warmup):
-        wl.step(ctx)
-    sampler = ClockSampler(local_rank)
+    main_res = measure(args.workload, args.steps, args.warmup, True)
+    extras = {}
+    for name in [e for e in args.extras.split(",") if e and e != args.workload]:
+        r = measure(name, max(3, min(args.steps, 20)), 3, False)
+        extras[name] = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "scaling", "roofline",
+                                          "gpu_launches")}
     if rank == 0:
-        sampler.start()
-    l0 = ctx.launches
-    total_ms = timed(wl.step, args.steps)
-    launches = ctx.launches - l0
-    clocks = sampler.stop() if rank == 0 else None
-    ms_per_step = total_ms / args.steps
-
-    # ---- the dominant kernel alone (no flush kernel between launches), same stream
-    kern_ms = ms_per_step
-    if wl.flush is not None:
-        # the flush kernel's own time, measured the same way, is taken out of the step
-        flush_ms = timed(lambda c: c.add(wl.flush, wl.flush, wl.flush), args.steps) / args.steps
-        kern_ms = max(ms_per_step - flush_ms, 1e-6)
-
-    # ---- end-to-end leg through the host-buffer entry point
-    e2e_steps = max(3, min(args.steps, 10))
-    wl.step_e2e(ctx)
-    e2e_ms = timed(wl.step_e2e, e2e_steps) / e2e_steps
-
-    pk = peaks()
-    value = wl.flop * world / (kern_ms * 1e-3) / 1e12
-    e2e_value = wl.flop * world / (e2e_ms * 1e-3) / 1e12
-    long_run = total_ms > 1000.0
-    if wl.bound == "tensor":
-        peak = pk["bf16_sustained"] if long_run else pk["bf16_burst"]
-        achieved = wl.flop / (kern_ms * 1e-3) / 1e12
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_kind": ("sustained" if long_run else "burst") + " cuBLAS bf16, of " + pk["source"]}
-    else:
-        achieved = wl.bytes / (kern_ms * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s", "frac": achieved / pk["hbm"],
-                "peak_kind": "STREAM-style copy, of " + pk["source"]}
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(wl.name)
-    roof["kernel"] = wl.kernel
-    roof["kernel_ms"] = kern_ms
-
-    if rank == 0:
-        line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": wl.desc, "parallelism": "replicas only" if world > 1 else "single GPU",
-                           "l2": wl.flush_note, "seed": SEED},
-                "roofline": roof,
-                "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
-                        "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms},
-                "gpu_launches": launches, "clocks": clocks}
-        if world == 1 and not args.no_cpu_baseline:
-            import oracle
-            v, sample = wl.cpu_sample()
-            line["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
-                                    "sample": sample}
+        line = {"metric": main_res["metric"], "value": main_res["value"], "unit": main_res["unit"], "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"],
+                "higher_is_better": True, "scaling": main_res["scaling"], "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": main_res["workload"],
+                           "parallelism": ("tp%d" % world if main_res["scaling"] == "strong" else
+                                           ("replicas only" if world > 1 else "single GPU")),
+                           "l2": main_res["l2"], "seed": SEED},
+                "roofline": main_res["roofline"], "e2e": main_res["e2e"], "gpu_launches": main_res["gpu_launches"],
+                "clocks": main_res["clocks"], "extras": extras}
+        if "cpu_baseline" in main_res:
+            line["cpu_baseline"] = main_res["cpu_baseline"]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    ctx.close()
 
 
 if __name__ == "__main__":

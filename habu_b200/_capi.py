@@ -99,6 +99,7 @@ def load() -> C.CDLL:
         "hb_graph_add": [vp, C.POINTER(hb_node)],
         "hb_graph_plan": [vp, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
         "hb_graph_run": [vp],
+        "hb_graph_run_timed": [vp, C.POINTER(C.c_float), i32],
         "hb_graph_describe": [vp, C.c_char_p, C.c_size_t],
         "hb_graph_tensor_ptr": [vp, i32, C.POINTER(vp)],
         "hb_autotune": [vp, C.POINTER(hb_op_desc), i32, C.POINTER(hb_tune_result)],

@@ -86,9 +86,24 @@ rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain, uint
 }
 
 // ------------------------------------------------------------------ RoPE (rotate-half)
-// One thread per (token, head, 8 consecutive pair indices): loads 16 B from each half.
-__global__ void rope_kernel(__nv_bfloat16* x, int64_t tokens, int seq, int heads, int head_dim,
-                            int64_t row_stride, float log2_base, int64_t pos0) {
+// cos/sin of pos * base^(-2i/d) are tabulated once per (seq, head_dim, base, pos0): the
+// angle is formed in double and reduced by sincos in double, so the table carries no
+// large-angle error.  table[p * half + i] = (cos, sin).
+__global__ void rope_table_kernel(float2* table, int seq, int half, int head_dim, double log2_base, int64_t pos0) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= seq * half) return;
+  const int i = idx % half;
+  const double pos = (double)(pos0 + idx / half);
+  const double th = pos * exp2(-2.0 * i / head_dim * log2_base);
+  double s, c;
+  sincos(th, &s, &c);
+  table[idx] = make_float2((float)c, (float)s);
+}
+
+// One thread per (token, head, 8 consecutive pair indices): 16 B from each half of the
+// head and 64 B of table.  Traffic: the rotated slice once in, once out.
+__global__ void rope_kernel(__nv_bfloat16* x, const float2* __restrict__ table, int64_t tokens, int seq, int heads,
+                            int head_dim, int64_t row_stride) {
   const int half = head_dim >> 1;
   const int groups = half >> 3;
   const int64_t total = tokens * heads * groups;
@@ -97,7 +112,7 @@ __global__ void rope_kernel(__nv_bfloat16* x, int64_t tokens, int seq, int heads
     const int g = (int)(idx % groups);
     const int h = (int)((idx / groups) % heads);
     const int64_t t = idx / ((int64_t)groups * heads);
-    const double pos = (double)(pos0 + t % seq);
+    const float4* cs = reinterpret_cast<const float4*>(table + (t % seq) * half + g * 8);
     __nv_bfloat16* base = x + t * row_stride + (int64_t)h * head_dim + g * 8;
     uint4 lo = *reinterpret_cast<uint4*>(base);
     uint4 hi = *reinterpret_cast<uint4*>(base + half);
@@ -107,15 +122,9 @@ __global__ void rope_kernel(__nv_bfloat16* x, int64_t tokens, int seq, int heads
     for (int k = 0; k < 4; ++k) {
       const float2 a = bf2_to_f2(lw[k]);
       const float2 b = bf2_to_f2(hw[k]);
-      float c0, s0, c1, s1;
-      const int i0 = g * 8 + 2 * k;
-      // theta = pos * base^(-2i/d); the angle is formed in double, reduced by sincosf
-      const float th0 = (float)(pos * exp2(-2.0 * i0 / head_dim * (double)log2_base));
-      const float th1 = (float)(pos * exp2(-2.0 * (i0 + 1) / head_dim * (double)log2_base));
-      sincosf(th0, &s0, &c0);
-      sincosf(th1, &s1, &c1);
-      lw[k] = f2_to_bf2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
-      hw[k] = f2_to_bf2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+      const float4 t4 = __ldg(cs + k);           // (c0, s0, c1, s1)
+      lw[k] = f2_to_bf2(a.x * t4.x - b.x * t4.y, a.y * t4.z - b.y * t4.w);
+      hw[k] = f2_to_bf2(b.x * t4.x + a.x * t4.y, b.y * t4.z + a.y * t4.w);
     }
     *reinterpret_cast<uint4*>(base) = lo;
     *reinterpret_cast<uint4*>(base + half) = hi;
@@ -264,10 +273,28 @@ extern "C" hb_status hb_rope(hb_ctx* ctx, void* x, int64_t tokens, int64_t seq, 
     return hb_fail(ctx, HB_ERR_UNSUPPORTED, "rope: head_dim must be a multiple of 16 and rows 16-byte aligned");
   if (row_stride < heads * head_dim) return hb_fail(ctx, HB_ERR_INVALID, "rope: row stride smaller than heads * head_dim");
   if (!(base > 1.0f)) return hb_fail(ctx, HB_ERR_INVALID, "rope: base must exceed 1");
+  if (seq > (1 << 22)) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "rope: sequence too long");
+  const int half = (int)head_dim / 2;
+  if (!ctx->rope_table || ctx->rope_seq != seq || ctx->rope_head_dim != head_dim || ctx->rope_base != base ||
+      ctx->rope_pos0 != pos0) {
+    const size_t bytes = (size_t)seq * half * sizeof(float2);
+    cudaError_t e = cudaSetDevice(ctx->device);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaSetDevice");
+    if (bytes > ctx->rope_table_bytes) {
+      if (ctx->rope_table) { cudaStreamSynchronize(ctx->stream); cudaFree(ctx->rope_table); ctx->rope_table = nullptr; }
+      e = cudaMalloc(&ctx->rope_table, bytes);
+      if (e != cudaSuccess) { cudaGetLastError(); ctx->rope_table_bytes = 0; return hb_fail(ctx, HB_ERR_NOMEM, "rope: cannot allocate the angle table"); }
+      ctx->rope_table_bytes = bytes;
+    }
+    rope_table_kernel<<<(unsigned)((seq * half + 255) / 256), 256, 0, ctx->stream>>>(
+        static_cast<float2*>(ctx->rope_table), (int)seq, half, (int)head_dim, log2((double)base), pos0);
+    ctx->launches++;
+    ctx->rope_seq = seq; ctx->rope_head_dim = head_dim; ctx->rope_base = base; ctx->rope_pos0 = pos0;
+  }
   const int64_t work = tokens * heads * (head_dim / 16);
-  rope_kernel<<<grid_for(ctx, work, 256), 256, 0, ctx->stream>>>(static_cast<__nv_bfloat16*>(x), tokens, (int)seq,
-                                                                 (int)heads, (int)head_dim, row_stride,
-                                                                 log2f(base), pos0);
+  rope_kernel<<<grid_for(ctx, work, 256), 256, 0, ctx->stream>>>(static_cast<__nv_bfloat16*>(x),
+                                                                 static_cast<const float2*>(ctx->rope_table), tokens,
+                                                                 (int)seq, (int)heads, (int)head_dim, row_stride);
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "rope launch");
 }

@@ -297,11 +297,9 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
   return HB_OK;
 }
 
-extern "C" hb_status hb_graph_run(hb_graph* g) {
-  if (!g) return HB_ERR_INVALID;
+static hb_status run_node(hb_graph* g, int i) {
   hb_ctx* ctx = g->ctx;
-  if (!g->planned) return hb_fail(ctx, HB_ERR_INVALID, "graph: call hb_graph_plan before hb_graph_run");
-  for (int i = 0; i < (int)g->nodes.size(); ++i) {
+  {
     const hb_node& n = g->nodes[i];
     auto T = [&](int id) -> const hb_graph_tensor& { return g->tensors[id]; };
     hb_status st = HB_OK;
@@ -373,6 +371,39 @@ extern "C" hb_status hb_graph_run(hb_graph* g) {
     }
   }
   return HB_OK;
+}
+
+extern "C" hb_status hb_graph_run(hb_graph* g) {
+  if (!g) return HB_ERR_INVALID;
+  if (!g->planned) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: call hb_graph_plan before hb_graph_run");
+  for (int i = 0; i < (int)g->nodes.size(); ++i) {
+    hb_status st = run_node(g, i);
+    if (st != HB_OK) return st;
+  }
+  return HB_OK;
+}
+
+// Runs the graph once with a CUDA event between nodes and reports each node's device
+// time in milliseconds (ms[i] for node i, up to `n` entries).  Synchronises the stream.
+extern "C" hb_status hb_graph_run_timed(hb_graph* g, float* ms, int32_t n) {
+  if (!g || !ms) return HB_ERR_INVALID;
+  hb_ctx* ctx = g->ctx;
+  if (!g->planned) return hb_fail(ctx, HB_ERR_INVALID, "graph: call hb_graph_plan before hb_graph_run_timed");
+  const int count = (int)g->nodes.size();
+  std::vector<cudaEvent_t> ev(count + 1);
+  for (auto& e : ev)
+    if (cudaEventCreate(&e) != cudaSuccess) return hb_fail(ctx, HB_ERR_CUDA, "graph: cannot create events");
+  hb_status st = HB_OK;
+  cudaEventRecord(ev[0], ctx->stream);
+  for (int i = 0; i < count && st == HB_OK; ++i) {
+    st = run_node(g, i);
+    cudaEventRecord(ev[i + 1], ctx->stream);
+  }
+  if (st == HB_OK) st = hb_sync(ctx);
+  if (st == HB_OK)
+    for (int i = 0; i < count && i < n; ++i) cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]);
+  for (auto& e : ev) cudaEventDestroy(e);
+  return st;
 }
 
 // Text listing of the planned graph: one line per node, then one per planner-owned

@@ -19,6 +19,8 @@ enum { HB_KTAG_GEMM = 1, HB_KTAG_ATTN = 2, HB_KTAG_ALLREDUCE = 3, HB_KTAG_SPLITK
 // Scratch slots: kernel workspace (split-K partials), host-call staging, autotune operands.
 enum { HB_SCRATCH_WORKSPACE = 0, HB_SCRATCH_STAGING = 1, HB_SCRATCH_TUNE = 2, HB_NUM_SCRATCH = 3 };
 
+constexpr int HB_MAX_SPLITK_TILES = 4096;
+
 struct hb_tune_entry {
   int32_t config_id;
   float ms;
@@ -40,6 +42,7 @@ struct hb_ctx {
   cudaStream_t own_stream = nullptr;  // created by the context
   int32_t* d_status = nullptr;
   int32_t* h_status = nullptr;        // pinned
+  int* d_tickets = nullptr;           // split-K arrival tickets, one per output tile, zero between launches
   int64_t launches = 0;
   std::string err;
   std::map<std::string, hb_tune_entry> tune_cache;
@@ -51,6 +54,11 @@ struct hb_ctx {
   void* scratch[HB_NUM_SCRATCH] = {};
   size_t scratch_bytes[HB_NUM_SCRATCH] = {};
   std::vector<void*> allocations;
+  // RoPE angle table (cos, sin) for the last (seq, head_dim, base, pos0) used
+  void* rope_table = nullptr;
+  size_t rope_table_bytes = 0;
+  int64_t rope_seq = 0, rope_head_dim = 0, rope_pos0 = 0;
+  float rope_base = 0.f;
 };
 
 hb_status hb_fail(hb_ctx* ctx, hb_status code, const char* fmt, ...);
@@ -81,3 +89,10 @@ struct hb_gemm_args {
 hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id);
 hb_status hb_launch_gemm_f32(hb_ctx* ctx, const hb_gemm_args& a);
 int hb_gemm_pick_config(hb_ctx* ctx, const hb_gemm_args& a);
+// Split-K path for M <= 64 (decode-shaped) products.
+bool hb_gemm_skinny_applicable(const hb_gemm_args& a);
+hb_status hb_launch_gemm_skinny(hb_ctx* ctx, const hb_gemm_args& a);
+void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int* split, int* kb_per_split,
+                         size_t* partial_floats, int* tiles);
+hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_gemm_args& a, float* partial, int* tickets,
+                                    int split, int kb_per_split, int tiles, int32_t* status);

@@ -43,6 +43,8 @@ extern "C" hb_status hb_ctx_create(int32_t device, hb_ctx** out) {
   if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&ctx->d_status, 4 * sizeof(int32_t)) != cudaSuccess ||
       cudaMemset(ctx->d_status, 0, 4 * sizeof(int32_t)) != cudaSuccess ||
+      cudaMalloc(&ctx->d_tickets, HB_MAX_SPLITK_TILES * sizeof(int)) != cudaSuccess ||
+      cudaMemset(ctx->d_tickets, 0, HB_MAX_SPLITK_TILES * sizeof(int)) != cudaSuccess ||
       cudaMallocHost(&ctx->h_status, 4 * sizeof(int32_t)) != cudaSuccess) {
     delete ctx;
     return HB_ERR_CUDA;
@@ -60,6 +62,8 @@ extern "C" hb_status hb_ctx_destroy(hb_ctx* ctx) {
   for (void* p : ctx->allocations) cudaFree(p);
   for (void* p : ctx->scratch)
     if (p) cudaFree(p);
+  if (ctx->rope_table) cudaFree(ctx->rope_table);
+  if (ctx->d_tickets) cudaFree(ctx->d_tickets);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -266,6 +270,7 @@ extern "C" hb_status hb_matmul(hb_ctx* ctx, const hb_tensor* A, const hb_tensor*
   if ((g.lda & 7) || (g.ldb & 7))
     return hb_fail(ctx, HB_ERR_UNSUPPORTED,
                    "matmul: bf16 operand leading dimensions must be multiples of 8 elements");
+  if (!(opts && opts->config_id >= 0) && hb_gemm_skinny_applicable(g)) return hb_launch_gemm_skinny(ctx, g);
   int cfg = (opts && opts->config_id >= 0) ? opts->config_id : hb_gemm_pick_config(ctx, g);
   return hb_launch_gemm_bf16(ctx, g, cfg);
 }

@@ -102,6 +102,12 @@ class Graph:
     def run(self):
         self.ctx._check(_lib.hb_graph_run(self._h))
 
+    def run_timed(self, n_nodes: int):
+        """One run with per-node device timing; returns a list of milliseconds."""
+        ms = (C.c_float * n_nodes)()
+        self.ctx._check(_lib.hb_graph_run_timed(self._h, ms, n_nodes))
+        return list(ms)
+
     def describe(self) -> str:
         buf = C.create_string_buffer(1 << 16)
         self.ctx._check(_lib.hb_graph_describe(self._h, buf, len(buf)))

@@ -200,6 +200,8 @@ hb_status hb_graph_view(hb_graph* g, int32_t base, int64_t offset, int32_t rank,
 hb_status hb_graph_add(hb_graph* g, const hb_node* node);
 hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* symmetric_bytes);
 hb_status hb_graph_run(hb_graph* g);
+/* One run with a CUDA event between nodes: ms[i] = device time of node i (first n nodes). */
+hb_status hb_graph_run_timed(hb_graph* g, float* ms, int32_t n);
 hb_status hb_graph_describe(hb_graph* g, char* buf, size_t len);
 hb_status hb_graph_tensor_ptr(hb_graph* g, int32_t id, void** ptr);
 

@@ -51,6 +51,18 @@ def test_bf16_ragged_shapes(ctx, M, N, K):
     assert max_abs(got, ref) < TOL_BF16
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 8192, 8192), (1, 256, 512), (7, 1000, 1096), (33, 4096, 2048), (64, 384, 8192)])
+def test_bf16_skinny_split_k_path(ctx, M, N, K):
+    # M <= 64 takes the swapped-operand split-K kernel; its slice-ordered reduction is
+    # deterministic, so two runs agree bit for bit
+    got, ref = run_bf16(ctx, M, N, K)
+    assert max_abs(got, ref) < TOL_BF16
+    again, _ = run_bf16(ctx, M, N, K)
+    assert np.array_equal(got, again)
+    forced, _ = run_bf16(ctx, M, N, K, config_id=4)      # the general kernel on the same shape
+    assert max_abs(forced, ref) < TOL_BF16
+
+
 def test_bf16_every_config(ctx):
     for i, cfg in enumerate(hb.matmul_configs()):
         got, ref = run_bf16(ctx, 384, 768, 320, config_id=i)
