@@ -75,6 +75,8 @@ def load() -> C.CDLL:
         "hb_sync": [vp],
         "hb_matmul": [vp, T, T, T, C.POINTER(hb_matmul_opts)],
         "hb_matmul_host": [vp, vp, vp, vp, i64, i64, i64, i32],
+        "hb_matmul_skinny_static": [vp, vp, vp, i64, i64, i64, i32, vp],
+        "hb_static_status": [i32, C.POINTER(i32)],
         "hb_attention": [vp, T, T, T, T, C.POINTER(hb_attn_opts)],
         "hb_attention_host": [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, f32],
         "hb_rmsnorm": [vp, vp, vp, vp, vp, i64, i64, f32],
@@ -113,6 +115,8 @@ def load() -> C.CDLL:
         fn.restype = i32
     lib.hb_last_error_string.argtypes = [vp]
     lib.hb_last_error_string.restype = C.c_char_p
+    lib.hb_static_last_error.argtypes = []
+    lib.hb_static_last_error.restype = C.c_char_p
     lib.hb_launch_count.argtypes = [vp]
     lib.hb_launch_count.restype = i64
     lib.hb_sm_count.argtypes = [vp]

@@ -298,3 +298,127 @@ hb_status hb_launch_gemm_skinny(hb_ctx* ctx, const hb_gemm_args& a) {
   if (st == HB_OK) ctx->launches++;
   return st;
 }
+
+// ---------------------------------------------------------------------------------------
+// hb_matmul_skinny_static: the skinny GEMM for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a
+// product: a real-time serving loop that forbids allocator locks and the implicit device
+// synchronisation cudaMalloc/cudaFree can cause; a foreign-runtime finaliser or signal
+// path (an OCaml stub running under the runtime lock, say) where a blocking driver call is
+// not allowed; a process whose memory budget was fixed at start-up and handed out in full.
+// For them the split-K scratch lives in the file-scope arrays below instead of in a
+// context-owned buffer.  Every GPU that loads the library carries these arrays (about
+// 4 MiB) until the process exits.
+//
+// Limits: partials split * ceil(N/128)*128 * Mpad <= HB_STATIC_MAX_PARTIAL_FLOATS and
+// ceil(N/128) <= HB_STATIC_MAX_TILES; larger problems are refused with HB_ERR_UNSUPPORTED.
+// The first call on a device resolves the arrays' device addresses and sets the kernel's
+// shared-memory attribute; it should come before any stream capture.
+// All calls share the arrays: two calls that overlap on the GPU (different streams) race
+// on the partials and tickets, so serialise them.  The tickets must start at zero and are
+// cleared on the stream before every launch; the partials need no clearing because every
+// slot read is written first in the same launch.
+// ---------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace {
+
+constexpr size_t HB_STATIC_MAX_PARTIAL_FLOATS = size_t(1) << 20;   // 4 MiB
+constexpr int HB_STATIC_MAX_TILES = 1024;
+
+static __device__ __align__(256) float g_static_partial[HB_STATIC_MAX_PARTIAL_FLOATS];
+static __device__ __align__(256) int g_static_tickets[HB_STATIC_MAX_TILES];
+static __device__ __align__(256) int32_t g_static_status[4];
+
+struct StaticDev {
+  bool ready = false;
+  float* partial = nullptr;
+  int* tickets = nullptr;
+  int32_t* status = nullptr;
+  int sm_count = 0;
+};
+StaticDev g_static_dev[64];
+std::mutex g_static_mu;
+thread_local char g_static_err[256] = "";
+
+hb_status static_fail(hb_status code, const char* msg, const char* detail = "") {
+  snprintf(g_static_err, sizeof(g_static_err), "%s%s", msg, detail);
+  return code;
+}
+
+// In host code the array names above are host-side stand-ins, not device addresses; the
+// address a kernel can use comes from cudaGetSymbolAddress, per device, with that device
+// current.
+hb_status static_setup(int device, StaticDev** out) {
+  if (device < 0 || device >= 64) return static_fail(HB_ERR_INVALID, "skinny_static: device index out of range");
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticDev& d = g_static_dev[device];
+  if (!d.ready) {
+    cudaError_t e;
+    if ((e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.partial), g_static_partial)) != cudaSuccess ||
+        (e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.tickets), g_static_tickets)) != cudaSuccess ||
+        (e = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_static_status)) != cudaSuccess)
+      return static_fail(HB_ERR_CUDA, "skinny_static: cudaGetSymbolAddress: ", cudaGetErrorString(e));
+    int major = 0;
+    if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess)
+      return static_fail(HB_ERR_CUDA, "skinny_static: cudaDeviceGetAttribute: ", cudaGetErrorString(e));
+    if (major != 10) return static_fail(HB_ERR_UNSUPPORTED, "skinny_static: an sm_100 GPU is required");
+    d.ready = true;
+  }
+  *out = &d;
+  return HB_OK;
+}
+
+}  // namespace
+
+extern "C" const char* hb_static_last_error(void) { return g_static_err; }
+
+extern "C" hb_status hb_matmul_skinny_static(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                             int32_t device, void* cuda_stream) {
+  g_static_err[0] = 0;
+  if (!A || !B || !C) return static_fail(HB_ERR_INVALID, "skinny_static: null pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return static_fail(HB_ERR_INVALID, "skinny_static: empty dimension");
+  if (M > MAX_MPAD) return static_fail(HB_ERR_UNSUPPORTED, "skinny_static: M must be at most 64");
+  if (K % 8 || N % 8) return static_fail(HB_ERR_UNSUPPORTED, "skinny_static: N and K must be multiples of 8");
+  if (N > INT32_MAX || K > INT32_MAX) return static_fail(HB_ERR_UNSUPPORTED, "skinny_static: dimension exceeds 2^31-1");
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess || cur != device)
+    return static_fail(HB_ERR_INVALID, "skinny_static: `device` must be the current CUDA device of the calling thread");
+  StaticDev* d = nullptr;
+  hb_status st = static_setup(device, &d);
+  if (st != HB_OK) return st;
+  int split, per, tiles;
+  size_t floats;
+  hb_gemm_skinny_plan(d->sm_count, M, N, K, &split, &per, &floats, &tiles);
+  if (tiles > HB_STATIC_MAX_TILES || floats > HB_STATIC_MAX_PARTIAL_FLOATS) {
+    char detail[128];
+    snprintf(detail, sizeof(detail), "needs %zu partial floats over %d tiles; the static scratch holds %zu floats and %d tiles",
+             floats, tiles, HB_STATIC_MAX_PARTIAL_FLOATS, HB_STATIC_MAX_TILES);
+    return static_fail(HB_ERR_UNSUPPORTED, "skinny_static: problem exceeds the static scratch: ", detail);
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaMemsetAsync(d->tickets, 0, sizeof(int) * tiles, stream);
+  if (e != cudaSuccess) return static_fail(HB_ERR_CUDA, "skinny_static: cudaMemsetAsync: ", cudaGetErrorString(e));
+  hb_gemm_args a;
+  memset(&a, 0, sizeof(a));
+  a.A = A; a.B = B; a.C = C;
+  a.M = M; a.N = N; a.K = K;
+  a.lda = K; a.ldb = K; a.ldc = N;
+  st = hb_launch_gemm_skinny_raw(nullptr, stream, a, d->partial, d->tickets, split, per, tiles, d->status);
+  if (st != HB_OK) return static_fail(st, "skinny_static: launch failed (descriptor encoding or kernel launch)");
+  return HB_OK;
+}
+
+// Copies the static status words back (blocking): out[0] != 0 means a bounded wait inside
+// a static launch on `device` gave up since the last call.  Clears them.
+extern "C" hb_status hb_static_status(int32_t device, int32_t* out4) {
+  if (!out4) return HB_ERR_INVALID;
+  StaticDev* d = nullptr;
+  hb_status st = static_setup(device, &d);
+  if (st != HB_OK) return st;
+  cudaError_t e = cudaMemcpy(out4, d->status, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && out4[0] != 0) e = cudaMemset(d->status, 0, 4 * sizeof(int32_t));
+  return e == cudaSuccess ? HB_OK : static_fail(HB_ERR_CUDA, "skinny_static: status copy: ", cudaGetErrorString(e));
+}

@@ -100,6 +100,28 @@ hb_status hb_matmul(hb_ctx* ctx, const hb_tensor* A, const hb_tensor* B, hb_tens
 hb_status hb_matmul_host(hb_ctx* ctx, const void* A_host, const void* B_host, void* C_host,
                          int64_t M, int64_t N, int64_t K, int32_t dtype);
 
+/* Skinny matmul (M <= 64) for callers that cannot allocate device memory when they need
+ * the product -- a latency-critical serving loop that bans allocator locks and the device
+ * synchronisation cudaMalloc/cudaFree may imply, a foreign-runtime callback that must not
+ * block in the driver, or a process whose device memory was handed out in full at start-up.
+ * This entry point has no counterpart in the reference and needs no hb_ctx: the split-K
+ * scratch is a static device array inside the library (about 4 MiB per GPU, held until
+ * the process exits).  A [M,K] row-major, B column-major (N rows of K), C [M,N] row-major,
+ * all bf16 device pointers; `device` must be the calling thread's current device and
+ * `cuda_stream` a cudaStream_t (NULL = default stream).  Asynchronous.
+ *   - Limit: split * ceil(N/128)*128 * roundup16(M) <= 2^20 partial floats and at most
+ *     1024 column tiles; anything larger returns HB_ERR_UNSUPPORTED with a message.
+ *   - The first call on a device looks up the static arrays' device addresses and sets
+ *     the kernel's shared-memory attribute; make that first call before any stream capture.
+ *   - All calls share the scratch: calls that overlap on the GPU race; serialise them.
+ *   - It calls no cudaMalloc, cudaFree or allocating library routine.
+ * hb_static_last_error returns the calling thread's last message; hb_static_status copies
+ * back (blocking) and clears the device-side status words of the static launches. */
+hb_status hb_matmul_skinny_static(const void* A, const void* B, void* C, int64_t M, int64_t N,
+                                  int64_t K, int32_t device, void* cuda_stream);
+const char* hb_static_last_error(void);
+hb_status hb_static_status(int32_t device, int32_t* out4);
+
 /* ---- model-IR attention node --------------------------------------------------------
  * O = softmax(scale * Q K^T + causal mask) V per (batch, head).  Tensors are
  * [batch, seq, heads, head_dim] bf16 (token-major); n_q_heads must be a multiple of
