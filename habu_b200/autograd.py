@@ -1,0 +1,128 @@
+"""Reverse-mode differentiation over the model-IR nodes the training configuration uses
+(matmul against a weight, GELU, MSE), and a data-parallel Adam trainer on top of it.
+
+A :class:`Tape` records the forward nodes as they are launched; :meth:`Tape.backward`
+replays them in reverse and launches the gradient kernels.  Every tensor stays on the
+device; weights are kept as fp32 masters with fp32 Adam moments and a bf16 compute copy,
+gradients are bf16 (also on the wire when data-parallel ranks sum them).
+
+Weight layout: ``W`` is ``[out_features, in_features]`` row-major, i.e. the column-major
+B operand of ``y = x @ W^T``.  The backward products reuse the same buffers through
+strided views: ``dX = dY @ W`` reads W as an N-contiguous B operand and
+``dW = dY^T @ X`` reads dY as an M-contiguous A operand, so no transposition pass runs.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import numpy as np
+
+from . import _capi
+from .model_ir import Context, Tensor
+
+
+class Tape:
+    def __init__(self, ctx: Context):
+        self.ctx = ctx
+        self.ops = []
+
+    # -- forward nodes ------------------------------------------------------------
+    def linear(self, x: Tensor, w_bf16: Tensor, out: Tensor, grad_w: Tensor, need_dx: bool = True) -> Tensor:
+        """out[B, out] = x[B, in] @ W^T with W [out, in]."""
+        self.ctx.matmul(x, w_bf16.T, out=out)
+        self.ops.append(("linear", x, w_bf16, out, grad_w, need_dx))
+        return out
+
+    def gelu(self, z: Tensor, out: Tensor) -> Tensor:
+        self.ctx.gelu(z, out=out)
+        self.ops.append(("gelu", z, out))
+        return out
+
+    def mse(self, y: Tensor, target: Tensor, dy: Tensor, loss: Tensor):
+        self.ctx.mse(y, target, dy=dy, loss=loss)
+        self.ops.append(("mse", y, dy))
+        return loss
+
+    # -- backward -------------------------------------------------------------------
+    def backward(self, scratch: List[Tensor], on_grad=None):
+        """Launches the gradient kernels.  `scratch` holds two [B, width] bf16 buffers used
+        alternately for activation gradients.  `on_grad(grad_w)` is called right after each
+        weight gradient is enqueued (the data-parallel trainer sums it there)."""
+        ctx = self.ctx
+        grads = {}                      # id(tensor) -> gradient tensor
+        k = 0
+        for op in reversed(self.ops):
+            if op[0] == "mse":
+                _, y, dy = op
+                grads[id(y)] = dy
+            elif op[0] == "gelu":
+                _, z, out = op
+                dout = grads[id(out)]
+                dz = scratch[k % 2]
+                k += 1
+                ctx.gelu_backward(z, dout, out=ctx.wrap(dz.ptr, z.shape))
+                grads[id(z)] = ctx.wrap(dz.ptr, z.shape)
+            else:
+                _, x, w, out, grad_w, need_dx = op
+                dout = grads[id(out)]
+                # dW[out, in] = dY^T[out, B] @ X[B, in]
+                ctx.matmul(dout.T, x, out=grad_w)
+                if on_grad:
+                    on_grad(grad_w)
+                if need_dx:
+                    dx = scratch[k % 2]
+                    k += 1
+                    # dX[B, in] = dY[B, out] @ W[out, in]
+                    ctx.matmul(dout, w, out=ctx.wrap(dx.ptr, x.shape))
+                    grads[id(x)] = ctx.wrap(dx.ptr, x.shape)
+        self.ops.clear()
+
+
+class MlpTrainer:
+    """n-layer MLP (no biases, GELU between layers, none after the last), MSE loss, Adam."""
+
+    def __init__(self, ctx: Context, width: int, batch: int, n_layers: int, weights_f32: List[np.ndarray],
+                 world: int = 1, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, grads_base_ptr: Optional[int] = None,
+                 algo: int = _capi.HB_AR_AUTO):
+        self.ctx, self.width, self.batch, self.n, self.world = ctx, width, batch, n_layers, world
+        self.lr, self.b1, self.b2, self.eps, self.algo = lr, beta1, beta2, eps, algo
+        self.step_no = 0
+        import oracle  # noqa: F401  (host-side bf16 conversion of the initial weights only)
+        from oracle import to_bf16_bits
+        self.w32 = [ctx.upload(np.ascontiguousarray(w, np.float32)) for w in weights_f32]
+        self.wb = [ctx.upload(to_bf16_bits(w)) for w in weights_f32]
+        zeros = np.zeros((width, width), np.float32)
+        self.m = [ctx.upload(zeros) for _ in range(n_layers)]
+        self.v = [ctx.upload(zeros) for _ in range(n_layers)]
+        gbytes = width * width * 2
+        if grads_base_ptr is None:
+            self.grads = [ctx.empty((width, width)) for _ in range(n_layers)]
+        else:   # gradients live in the peer-mapped buffer so the allreduce runs in place
+            self.grads = [ctx.wrap(grads_base_ptr + i * gbytes, (width, width)) for i in range(n_layers)]
+        self.z = [ctx.empty((batch, width)) for _ in range(n_layers)]
+        self.h = [ctx.empty((batch, width)) for _ in range(n_layers - 1)]
+        self.scratch = [ctx.empty((batch, width)) for _ in range(2)]
+        self.dy = ctx.empty((batch, width))
+        self.loss = ctx.empty((1,), _capi.HB_F32)
+
+    @staticmethod
+    def grad_bytes(width: int, n_layers: int) -> int:
+        return n_layers * width * width * 2
+
+    def step(self, x: Tensor, y: Tensor):
+        """One forward + backward + (allreduce) + Adam step; everything is enqueued."""
+        ctx = self.ctx
+        tape = Tape(ctx)
+        h = x
+        for i in range(self.n):
+            tape.linear(h, self.wb[i], self.z[i], self.grads[i], need_dx=i > 0)
+            if i < self.n - 1:
+                h = tape.gelu(self.z[i], self.h[i])
+        tape.mse(self.z[-1], y, self.dy, self.loss)
+        on_grad = (lambda g: ctx.all_reduce(g, self.algo)) if self.world > 1 else None
+        tape.backward(self.scratch, on_grad)
+        self.step_no += 1
+        for i in range(self.n):
+            ctx.adam_step(self.w32[i], self.m[i], self.v[i], self.grads[i], self.wb[i], self.step_no, self.lr, self.b1,
+                          self.b2, self.eps, 1.0 / self.world)
+        return self.loss

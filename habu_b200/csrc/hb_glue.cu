@@ -362,3 +362,97 @@ extern "C" hb_status hb_argmax(hb_ctx* ctx, const void* x, int32_t* out, int64_t
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "argmax launch");
 }
+
+// ------------------------------------------------------------------ MSE loss and Adam
+namespace {
+
+// dY = 2 (y - t) / n (bf16), per-block partial sums of (y - t)^2 in fixed slots.
+__global__ void __launch_bounds__(256)
+mse_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ t, __nv_bfloat16* __restrict__ dy,
+           float* __restrict__ partial, int64_t n, float two_over_n) {
+  __shared__ float red[8];
+  float s = 0.f;
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    const float d = __bfloat162float(y[i]) - __bfloat162float(t[i]);
+    s += d * d;
+    dy[i] = __float2bfloat16_rn(d * two_over_n);
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    partial[blockIdx.x] = tot;
+  }
+}
+// loss = sum(partial[0..m)) / n, added in index order by one warp (deterministic).
+__global__ void mse_finish_kernel(const float* __restrict__ partial, int m, float inv_n, float* __restrict__ loss) {
+  double s = 0.0;
+  for (int i = threadIdx.x; i < m; i += 32) s += (double)partial[i];
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (threadIdx.x == 0) *loss = (float)(s * (double)inv_n);
+}
+
+// Bias-corrected Adam on fp32 master weights and moments; the gradient arrives in bf16
+// (scaled by grad_scale, e.g. 1/world after a sum-allreduce) and the bf16 compute copy of
+// the weights is refreshed in the same pass: 2 + 12 bytes read, 12 + 2 written per weight.
+__global__ void __launch_bounds__(256)
+adam_kernel(float4* __restrict__ w, float4* __restrict__ m, float4* __restrict__ v, const uint2* __restrict__ g,
+            uint2* __restrict__ wb, int64_t n4, float lr, float b1, float b2, float eps, float c1, float c2,
+            float grad_scale) {
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n4; i += (int64_t)gridDim.x * 256) {
+    const uint2 gr = g[i];
+    const float2 g01 = bf2_to_f2(gr.x), g23 = bf2_to_f2(gr.y);
+    const float gv[4] = {g01.x * grad_scale, g01.y * grad_scale, g23.x * grad_scale, g23.y * grad_scale};
+    float4 wv = w[i], mv = m[i], vv = v[i];
+    float* wp = reinterpret_cast<float*>(&wv);
+    float* mp = reinterpret_cast<float*>(&mv);
+    float* vp = reinterpret_cast<float*>(&vv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      mp[k] = b1 * mp[k] + (1.0f - b1) * gv[k];
+      vp[k] = b2 * vp[k] + (1.0f - b2) * gv[k] * gv[k];
+      const float mh = mp[k] / c1, vh = vp[k] / c2;
+      wp[k] = wp[k] - lr * mh / (sqrtf(vh) + eps);
+    }
+    w[i] = wv; m[i] = mv; v[i] = vv;
+    wb[i] = make_uint2(f2_to_bf2(wp[0], wp[1]), f2_to_bf2(wp[2], wp[3]));
+  }
+}
+
+}  // namespace
+
+extern "C" hb_status hb_mse(hb_ctx* ctx, const void* y, const void* target, void* dy, float* loss, int64_t n) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!y || !target || !dy || !loss) return hb_fail(ctx, HB_ERR_INVALID, "mse: null pointer");
+  if (n <= 0) return hb_fail(ctx, HB_ERR_INVALID, "mse: empty tensor");
+  const int grid = grid_for(ctx, n, 256);
+  void* ws = nullptr;
+  hb_status st = hb_get_scratch(ctx, HB_SCRATCH_REDUCE, (size_t)grid * sizeof(float), &ws);
+  if (st != HB_OK) return st;
+  mse_kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(target),
+                                            static_cast<__nv_bfloat16*>(dy), static_cast<float*>(ws), n, 2.0f / (float)n);
+  mse_finish_kernel<<<1, 32, 0, ctx->stream>>>(static_cast<const float*>(ws), grid, 1.0f / (float)n, loss);
+  ctx->launches += 2;
+  return hb_check_cuda(ctx, cudaGetLastError(), "mse launch");
+}
+
+extern "C" hb_status hb_adam_step(hb_ctx* ctx, float* w, float* m, float* v, const void* grad_bf16, void* w_bf16,
+                                  int64_t n, float lr, float beta1, float beta2, float eps, int64_t step,
+                                  float grad_scale) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!w || !m || !v || !grad_bf16 || !w_bf16) return hb_fail(ctx, HB_ERR_INVALID, "adam: null pointer");
+  if (n <= 0 || n % 4) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "adam: element count must be a positive multiple of 4");
+  if (step < 1) return hb_fail(ctx, HB_ERR_INVALID, "adam: step counts from 1");
+  if (!HB_ALIGNED16(w) || !HB_ALIGNED16(m) || !HB_ALIGNED16(v) || (reinterpret_cast<uintptr_t>(grad_bf16) & 7) ||
+      (reinterpret_cast<uintptr_t>(w_bf16) & 7))
+    return hb_fail(ctx, HB_ERR_INVALID, "adam: misaligned pointer");
+  const float c1 = (float)(1.0 - pow((double)beta1, (double)step));
+  const float c2 = (float)(1.0 - pow((double)beta2, (double)step));
+  adam_kernel<<<grid_for(ctx, n / 4, 256), 256, 0, ctx->stream>>>(
+      reinterpret_cast<float4*>(w), reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v),
+      static_cast<const uint2*>(grad_bf16), static_cast<uint2*>(w_bf16), n / 4, lr, beta1, beta2, eps, c1, c2, grad_scale);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "adam launch");
+}

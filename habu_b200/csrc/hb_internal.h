@@ -17,7 +17,7 @@
 enum { HB_KTAG_GEMM = 1, HB_KTAG_ATTN = 2, HB_KTAG_ALLREDUCE = 3, HB_KTAG_SPLITK = 4 };
 
 // Scratch slots: kernel workspace (split-K partials), host-call staging, autotune operands.
-enum { HB_SCRATCH_WORKSPACE = 0, HB_SCRATCH_STAGING = 1, HB_SCRATCH_TUNE = 2, HB_NUM_SCRATCH = 3 };
+enum { HB_SCRATCH_WORKSPACE = 0, HB_SCRATCH_STAGING = 1, HB_SCRATCH_TUNE = 2, HB_SCRATCH_REDUCE = 3, HB_NUM_SCRATCH = 4 };
 
 constexpr int HB_MAX_SPLITK_TILES = 4096;
 

@@ -245,6 +245,20 @@ class Context:
         self._check(_lib.hb_add(self._h, a.ptr, b.ptr, out.ptr, a.nbytes // 2))
         return out
 
+    def mse(self, y: Tensor, target: Tensor, dy: Optional[Tensor] = None, loss: Optional[Tensor] = None):
+        """Returns (loss tensor f32[1], dy) for mean((y - target)^2)."""
+        if dy is None:
+            dy = self.empty(y.shape, y.dtype)
+        if loss is None:
+            loss = self.empty((1,), HB_F32)
+        self._check(_lib.hb_mse(self._h, y.ptr, target.ptr, dy.ptr, loss.ptr, y.nbytes // 2))
+        return loss, dy
+
+    def adam_step(self, w: Tensor, m: Tensor, v: Tensor, grad: Tensor, w_bf16: Tensor, step: int, lr=1e-3, beta1=0.9,
+                  beta2=0.999, eps=1e-8, grad_scale=1.0):
+        self._check(_lib.hb_adam_step(self._h, w.ptr, m.ptr, v.ptr, grad.ptr, w_bf16.ptr, w.nbytes // 4, lr, beta1,
+                                      beta2, eps, step, grad_scale))
+
     def argmax(self, x: Tensor) -> Tensor:
         rows, cols = x.shape
         out = self.empty((rows,), HB_I32)

@@ -160,6 +160,15 @@ hb_status hb_gelu(hb_ctx* ctx, const void* x, void* y, int64_t n);
 /* dx = dy * gelu'(x) (erf-exact derivative). */
 hb_status hb_gelu_backward(hb_ctx* ctx, const void* x, const void* dy, void* dx, int64_t n);
 hb_status hb_add(hb_ctx* ctx, const void* a, const void* b, void* out, int64_t n);
+/* Mean-squared error over n bf16 elements: *loss (device fp32) = mean((y - target)^2),
+ * dy = 2 (y - target) / n (bf16).  Partial sums are added in a fixed order. */
+hb_status hb_mse(hb_ctx* ctx, const void* y, const void* target, void* dy, float* loss, int64_t n);
+/* One bias-corrected Adam step (no weight decay) on fp32 master weights w and moments m, v
+ * from a bf16 gradient scaled by grad_scale; also refreshes the bf16 copy of the weights.
+ * step counts from 1. */
+hb_status hb_adam_step(hb_ctx* ctx, float* w, float* m, float* v, const void* grad_bf16,
+                       void* w_bf16, int64_t n, float lr, float beta1, float beta2, float eps,
+                       int64_t step, float grad_scale);
 /* argmax over the last dimension, first index wins ties (bit-exact). */
 hb_status hb_argmax(hb_ctx* ctx, const void* x, int32_t* out, int64_t rows, int64_t cols);
 
