@@ -206,6 +206,7 @@ class DecoderWorkload:
     kernel = "hb_gemm_bf16_kernel"
     flush = None
     scaling = "strong"
+    collective = True
 
     def __init__(self, name="decoder"):
         from habu_b200.tp import DecoderConfig
@@ -283,7 +284,82 @@ class DecoderWorkload:
             f"the {self.cfg.n_layers}-layer block")
 
 
+class MlpWorkload:
+    """4-layer MLP forward + backward + Adam, width 8192, GELU, batch 4096 per GPU, MSE; bf16
+    activations / gradients, fp32 master weights and moments; data-parallel gradient allreduce."""
+    bound = "tensor"
+    kernel = "hb_gemm_bf16_kernel"
+    flush = None
+    scaling = "weak"
+    collective = True
+
+    def __init__(self, name="mlp", width=8192, batch=4096, layers=4):
+        self.name, self.width, self.batch, self.layers = name, width, batch, layers
+        fwd = layers * 2.0 * batch * width * width
+        self.flop = fwd + fwd + (layers - 1) * 2.0 * batch * width * width   # fwd + dW + dX (no dX for layer 0)
+        self.metric, self.unit = "mlp_train_samples_per_s", "samples/s"
+        self.desc = (f"{layers}-layer MLP fwd+bwd+Adam: width {width}, GELU, batch {batch} per GPU, MSE, Adam lr 1e-3 "
+                     "b=(0.9,0.999) eps 1e-8, bf16 activations and gradients, fp32 master weights and moments; "
+                     "data-parallel bf16 gradient allreduce")
+        self.flush_note = "weights, moments and activations per step (>4 GB) exceed L2"
+
+    def setup(self, ctx, rank, pinned, world=1, dist=None):
+        import oracle
+        from habu_b200.autograd import MlpTrainer
+        from oracle import mlp
+        ws = mlp.make_weights(self.width, self.layers)
+        base = None
+        if world > 1:
+            ids = [ctx.comm_unique_id() if rank == 0 else None]
+            dist.broadcast_object_list(ids, src=0)
+            ctx.comm_init_rank(world, rank, ids[0])
+            nbytes = MlpTrainer.grad_bytes(self.width, self.layers)
+            base, handle = ctx.p2p_alloc(nbytes)
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            ctx.p2p_attach(world, rank, handles, nbytes)
+        self.tr = MlpTrainer(ctx, self.width, self.batch, self.layers, ws, world=world, grads_base_ptr=base)
+        del ws
+        x, y = mlp.make_batch(self.batch, self.width, rank)
+        xb, yb = oracle.to_bf16_bits(x), oracle.to_bf16_bits(y)
+        self.hX, self.hY = pinned(xb), pinned(yb)
+        self.hL = pinned(np.zeros(1, np.float32))
+        self.dX, self.dY = ctx.upload(xb), ctx.upload(yb)
+        self.h2d, self.d2h = xb.nbytes + yb.nbytes, 4
+        self.world = world
+
+    def step(self, ctx):
+        self.tr.step(self.dX, self.dY)
+
+    def step_e2e(self, ctx):
+        DecoderWorkload._copy(ctx, self.dX.ptr, self.hX, up=True)
+        DecoderWorkload._copy(ctx, self.dY.ptr, self.hY, up=True)
+        self.tr.step(self.dX, self.dY)
+        DecoderWorkload._copy(ctx, self.tr.loss.ptr, self.hL, up=False)
+        ctx.sync()
+
+    def value(self, ms, world):
+        return self.batch * world / (ms * 1e-3)
+
+    def cpu_sample(self, max_rows=None):
+        """Bounded CPU sample: one fwd+bwd+Adam step at width 1024, batch 512 on the oracle."""
+        from oracle import mlp
+        width, batch = (1024, 512) if max_rows is None else (512, 256)
+        ws = mlp.make_weights(width, self.layers)
+        x, y = mlp.make_batch(batch, width)
+        m = [np.zeros_like(w) for w in ws]
+        v = [np.zeros_like(w) for w in ws]
+        t0 = time.perf_counter()
+        _, grads = mlp.forward_backward(ws, x, y, round_bf16=False)
+        mlp.adam_update(ws, m, v, grads, 1)
+        dt = time.perf_counter() - t0
+        scale = (batch * width * width) / (self.batch * self.width * self.width)   # flop ratio sample / full step
+        return self.batch * scale / dt, (f"one step at width {width}, batch {batch} (oracle, fp32), scaled by the flop "
+                                         f"ratio to samples/s of the width-{self.width} model")
+
+
 WORKLOADS = {
+    "mlp": lambda: MlpWorkload(),
     "attention": lambda: AttentionWorkload("attention", 8, 4096, 32),
     "decoder": lambda: DecoderWorkload(),
     "gemm": lambda: GemmWorkload("gemm", 8192, 8192, 8192),
@@ -360,7 +436,8 @@ def main():
         ctx = hb.Context(local_rank)
         ctx.set_stream(stream.cuda_stream)
         wl = WORKLOADS[name]()
-        sharded = getattr(wl, "scaling", "weak") == "strong"
+        sharded = getattr(wl, "collective", False)        # the step has a real exchange between ranks
+        strong = getattr(wl, "scaling", "weak") == "strong"
         if sharded:
             wl.setup(ctx, rank, pinned, world, dist)
         else:
@@ -403,7 +480,8 @@ def main():
             kern_ms = max(ms_per_step - flush_ms, 1e-6)
         if sharded:
             value = wl.value(kern_ms, world)
-            achieved = wl.flop / world / (kern_ms * 1e-3) / 1e12       # per-GPU share of the algorithmic work
+            # per-GPU share of the algorithmic work (strong scaling splits it, weak repeats it)
+            achieved = wl.flop / (world if strong else 1) / (kern_ms * 1e-3) / 1e12
         else:
             value = wl.flop * world / (kern_ms * 1e-3) / 1e12
             achieved = wl.flop / (kern_ms * 1e-3) / 1e12
@@ -454,7 +532,8 @@ def main():
                 "data": "synthetic",
                 "config": {"workload": main_res["workload"],
                            "parallelism": ("tp%d" % world if main_res["scaling"] == "strong" else
-                                           ("replicas only" if world > 1 else "single GPU")),
+                                           ("dp%d" % world if args.workload == "mlp" else
+                                            ("replicas only" if world > 1 else "single GPU"))),
                            "l2": main_res["l2"], "seed": SEED},
                 "roofline": main_res["roofline"], "e2e": main_res["e2e"], "gpu_launches": main_res["gpu_launches"],
                 "clocks": main_res["clocks"], "extras": extras}
