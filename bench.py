@@ -230,7 +230,9 @@ class DecoderWorkload:
             full = decoder.make_layer(cfg, i)
             layers.append({k: oracle.to_bf16_bits(v) for k, v in shard_layer(full, cfg, world, rank).items()})
             del full
-        self.dg = DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO)
+        # micro-batches whose allreduce overlaps the next chunk's GEMMs (only useful with peers)
+        self.chunks = int(os.environ.get("HB_DECODER_CHUNKS", "4" if world > 1 else "1"))
+        self.dg = DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO, self.chunks)
         _, sym = self.dg.plan()
         if world > 1:
             ids = [ctx.comm_unique_id() if rank == 0 else None]

@@ -53,7 +53,7 @@ class hb_tune_result(C.Structure):
 
 class hb_node(C.Structure):
     _fields_ = [("kind", C.c_int32), ("inputs", C.c_int32 * 4), ("out", C.c_int32),
-                ("iparam", C.c_int32 * 4), ("fparam", C.c_float * 2)]
+                ("iparam", C.c_int32 * 4), ("fparam", C.c_float * 2), ("stream", C.c_int32)]
 
 
 def load() -> C.CDLL:

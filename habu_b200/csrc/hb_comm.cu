@@ -15,6 +15,7 @@
 // Algorithmic bytes per rank: 2 * (world-1)/world * count * elem over NVLink.
 #include <dlfcn.h>
 #include <nccl.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "hb_internal.h"
@@ -59,7 +60,7 @@ NcclApi* nccl_api() {
 // ------------------------------------------------------------------ P2P two-shot kernel
 constexpr int AR_MAX_WORLD = 8;
 constexpr int AR_MAX_CTAS = 296;                       // 2 per SM on a 148-SM part
-constexpr int AR_THREADS = 512;
+constexpr int AR_THREADS = 256;
 constexpr size_t AR_FLAG_BYTES = 2 * AR_MAX_CTAS * AR_MAX_WORLD * sizeof(uint32_t);
 constexpr uint32_t AR_SPIN_LIMIT = 1u << 24;
 
@@ -149,8 +150,12 @@ struct Vec<__nv_bfloat16> {
   }
 };
 
-template <typename T>
-__global__ void __launch_bounds__(AR_THREADS)
+// WORLD is the unroll bound (2, 4 or 8; other rank counts run the 8-way body with the
+// absent ranks predicated off).  256 threads and at most 64 registers, so that a CTA of
+// this kernel fits on an SM next to a persistent GEMM CTA when the collective overlaps
+// compute on the side stream.
+template <typename T, int WORLD>
+__global__ void __launch_bounds__(AR_THREADS, 4)
 hb_allreduce_p2p_kernel(const ArParams p) {
   constexpr int N = Vec<T>::N;
   const int cta = blockIdx.x;
@@ -160,26 +165,20 @@ hb_allreduce_p2p_kernel(const ArParams p) {
   const int64_t per = (nvec + p.world - 1) / p.world;
   const int64_t v0 = per * p.rank;
   const int64_t v1 = min(nvec, v0 + per);
-  const uint4* src[AR_MAX_WORLD];
-  uint4* dst[AR_MAX_WORLD];
-#pragma unroll
-  for (int r = 0; r < AR_MAX_WORLD; ++r) {
-    src[r] = r < p.world ? reinterpret_cast<const uint4*>(static_cast<char*>(p.peers[r]) + p.data_off) : nullptr;
-    dst[r] = const_cast<uint4*>(src[r]);
-  }
   for (int64_t i = v0 + cta * (int64_t)AR_THREADS + threadIdx.x; i < v1; i += (int64_t)gridDim.x * AR_THREADS) {
-    uint4 v[AR_MAX_WORLD];
+    uint4 v[WORLD];
 #pragma unroll
-    for (int r = 0; r < AR_MAX_WORLD; ++r)
-      if (r < p.world) v[r] = src[r][i];           // peer loads over NVLink, all in flight
+    for (int r = 0; r < WORLD; ++r)
+      if (r < p.world)                             // peer loads over NVLink, all in flight
+        v[r] = *(reinterpret_cast<const uint4*>(static_cast<const char*>(p.peers[r]) + p.data_off) + i);
     float acc[N] = {};
 #pragma unroll
-    for (int r = 0; r < AR_MAX_WORLD; ++r)
+    for (int r = 0; r < WORLD; ++r)
       if (r < p.world) Vec<T>::add(acc, v[r]);      // fixed rank order: identical on every rank
     const uint4 out = Vec<T>::pack(acc);
 #pragma unroll
-    for (int r = 0; r < AR_MAX_WORLD; ++r)
-      if (r < p.world) dst[r][i] = out;
+    for (int r = 0; r < WORLD; ++r)
+      if (r < p.world) *(reinterpret_cast<uint4*>(static_cast<char*>(p.peers[r]) + p.data_off) + i) = out;
   }
   if (p.rank == 0 && cta == 0 && threadIdx.x < (int)(p.count % N)) {
     const int64_t e = nvec * N + threadIdx.x;
@@ -343,12 +342,23 @@ extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32
   const int64_t nvec = count / (16 / es);
   int64_t want = (nvec / s.world + AR_THREADS - 1) / AR_THREADS;
   int grid = (int)(want < 1 ? 1 : want);
-  const int cap = ctx->sm_count * 2 < AR_MAX_CTAS ? ctx->sm_count * 2 : AR_MAX_CTAS;
+  int cap = ctx->sm_count * 2 < AR_MAX_CTAS ? ctx->sm_count * 2 : AR_MAX_CTAS;
+  if (const char* e = getenv("HB_AR_MAX_CTAS")) {   // every rank must use the same value
+    const int v = atoi(e);
+    if (v >= 1 && v < cap) cap = v;
+  }
   if (grid > cap) grid = cap;
-  if (dtype == HB_BF16)
-    hb_allreduce_p2p_kernel<__nv_bfloat16><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
-  else
-    hb_allreduce_p2p_kernel<float><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+#define HB_AR_LAUNCH(T, W) hb_allreduce_p2p_kernel<T, W><<<grid, AR_THREADS, 0, ctx->stream>>>(p)
+  if (dtype == HB_BF16) {
+    if (s.world == 2) HB_AR_LAUNCH(__nv_bfloat16, 2);
+    else if (s.world <= 4) HB_AR_LAUNCH(__nv_bfloat16, 4);
+    else HB_AR_LAUNCH(__nv_bfloat16, 8);
+  } else {
+    if (s.world == 2) HB_AR_LAUNCH(float, 2);
+    else if (s.world <= 4) HB_AR_LAUNCH(float, 4);
+    else HB_AR_LAUNCH(float, 8);
+  }
+#undef HB_AR_LAUNCH
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "all_reduce launch");
 }

@@ -38,6 +38,12 @@ struct hb_graph {
   hb_ctx* ctx;
   std::vector<hb_graph_tensor> tensors;
   std::vector<hb_node> nodes;
+  // two-stream execution: nodes with stream == 1 run on the context's side stream
+  std::vector<int> wait_for;            // per node: index of the node on the other stream to wait for, or -1
+  std::vector<char> needs_event;        // per node: some node on the other stream waits for it
+  std::vector<cudaEvent_t> events;      // per node (created lazily for needs_event nodes)
+  cudaEvent_t fork_event = nullptr;
+  int last_side_node = -1;
   void* arena = nullptr;
   size_t arena_bytes = 0, symmetric_bytes = 0;
   bool planned = false;
@@ -93,11 +99,13 @@ extern "C" hb_status hb_graph_create(hb_ctx* ctx, hb_graph** out) {
 
 extern "C" hb_status hb_graph_destroy(hb_graph* g) {
   if (!g) return HB_ERR_INVALID;
-  if (g->arena) {
-    cudaSetDevice(g->ctx->device);
-    cudaStreamSynchronize(g->ctx->stream);
-    cudaFree(g->arena);
-  }
+  cudaSetDevice(g->ctx->device);
+  cudaStreamSynchronize(g->ctx->stream);
+  if (g->ctx->side_stream) cudaStreamSynchronize(g->ctx->side_stream);
+  if (g->arena) cudaFree(g->arena);
+  for (cudaEvent_t e : g->events)
+    if (e) cudaEventDestroy(e);
+  if (g->fork_event) cudaEventDestroy(g->fork_event);
   delete g;
   return HB_OK;
 }
@@ -291,6 +299,55 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
     t.ptr = r.ptr ? static_cast<char*>(r.ptr) + off * (int64_t)elem_size(r.dtype) : nullptr;
   }
   g->symmetric_bytes = totals[1];
+  // ---- cross-stream dependencies, on byte ranges (planner-owned tensors may share memory)
+  {
+    const int nn = (int)g->nodes.size();
+    struct Range { const char* lo; const char* hi; bool write; };
+    auto range_of = [&](int id, bool write) {
+      const hb_graph_tensor& t = g->tensors[id];
+      int64_t ext = 1;
+      for (int i = 0; i < t.rank; ++i) ext += (t.shape[i] - 1) * t.stride[i];
+      const char* lo = static_cast<const char*>(t.ptr);
+      return Range{lo, lo + ext * (int64_t)elem_size(t.dtype), write};
+    };
+    std::vector<std::vector<Range>> foot(nn);
+    bool any_side = false;
+    for (int i = 0; i < nn; ++i) {
+      const hb_node& n = g->nodes[i];
+      if (n.stream != 0) any_side = true;
+      for (int k = 0; k < 4; ++k)
+        if (n.in[k] >= 0) foot[i].push_back(range_of(n.in[k], n.kind == HB_NODE_RMSNORM && k == 2));
+      foot[i].push_back(range_of(n.out, true));
+    }
+    g->wait_for.assign(nn, -1);
+    g->needs_event.assign(nn, 0);
+    g->last_side_node = -1;
+    if (any_side) {
+      if (!ctx->side_stream) {
+        cudaError_t e = cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaStreamCreate(side)");
+      }
+      for (int i = 0; i < nn; ++i) {
+        if (g->nodes[i].stream != 0) g->last_side_node = i;
+        for (int j = i - 1; j >= 0; --j) {
+          if ((g->nodes[j].stream != 0) == (g->nodes[i].stream != 0)) continue;
+          bool conflict = false;
+          for (const Range& a : foot[i])
+            for (const Range& b : foot[j])
+              if ((a.write || b.write) && a.lo < b.hi && b.lo < a.hi) conflict = true;
+          if (conflict) { g->wait_for[i] = j; g->needs_event[j] = 1; break; }   // the latest one covers earlier ones
+        }
+      }
+      if (g->last_side_node >= 0) g->needs_event[g->last_side_node] = 1;
+      g->events.resize(nn, nullptr);
+      for (int i = 0; i < nn; ++i)
+        if (g->needs_event[i] && !g->events[i] &&
+            cudaEventCreateWithFlags(&g->events[i], cudaEventDisableTiming) != cudaSuccess)
+          return hb_fail(ctx, HB_ERR_CUDA, "graph: cannot create events");
+      if (!g->fork_event && cudaEventCreateWithFlags(&g->fork_event, cudaEventDisableTiming) != cudaSuccess)
+        return hb_fail(ctx, HB_ERR_CUDA, "graph: cannot create events");
+    }
+  }
   g->planned = true;
   if (arena_bytes) *arena_bytes = need;
   if (symmetric_bytes) *symmetric_bytes = totals[1];
@@ -376,11 +433,24 @@ static hb_status run_node(hb_graph* g, int i) {
 extern "C" hb_status hb_graph_run(hb_graph* g) {
   if (!g) return HB_ERR_INVALID;
   if (!g->planned) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: call hb_graph_plan before hb_graph_run");
-  for (int i = 0; i < (int)g->nodes.size(); ++i) {
-    hb_status st = run_node(g, i);
-    if (st != HB_OK) return st;
+  hb_ctx* ctx = g->ctx;
+  cudaStream_t main_stream = ctx->stream;
+  const bool two = g->last_side_node >= 0;
+  if (two) {   // the side stream starts after everything already queued on the main stream
+    cudaEventRecord(g->fork_event, main_stream);
+    cudaStreamWaitEvent(ctx->side_stream, g->fork_event, 0);
   }
-  return HB_OK;
+  hb_status st = HB_OK;
+  for (int i = 0; i < (int)g->nodes.size() && st == HB_OK; ++i) {
+    cudaStream_t s = (two && g->nodes[i].stream != 0) ? ctx->side_stream : main_stream;
+    if (two && g->wait_for[i] >= 0) cudaStreamWaitEvent(s, g->events[g->wait_for[i]], 0);
+    ctx->stream = s;
+    st = run_node(g, i);
+    ctx->stream = main_stream;
+    if (two && g->needs_event[i]) cudaEventRecord(g->events[i], s);
+  }
+  if (two) cudaStreamWaitEvent(main_stream, g->events[g->last_side_node], 0);   // join
+  return st;
 }
 
 // Runs the graph once with a CUDA event between nodes and reports each node's device

@@ -40,6 +40,7 @@ struct hb_ctx {
   int sm_count = 0;
   cudaStream_t stream = nullptr;      // stream in use
   cudaStream_t own_stream = nullptr;  // created by the context
+  cudaStream_t side_stream = nullptr; // second stream for executor nodes that overlap (collectives)
   int32_t* d_status = nullptr;
   int32_t* h_status = nullptr;        // pinned
   int* d_tickets = nullptr;           // split-K arrival tickets, one per output tile, zero between launches

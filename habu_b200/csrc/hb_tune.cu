@@ -1,7 +1,8 @@
 // Autotune entry point: times every candidate configuration of an operator for one
 // problem shape on the device, keeps the winner in the context's cache and persists the
 // cache as one text line per entry:
-//   <op> <dtype> <m> <n> <k> <layout> <epilogue> sm<count> w<world> = <config_id> <ms>
+//   <op> <dtype> <m> <n> <k> <layout> <epilogue> sm<count> = <config_id> <ms>
+// (m, n, k are the shapes one GPU computes, so a tensor-parallel shard has its own line).
 #include <stdio.h>
 #include <string.h>
 
@@ -27,9 +28,10 @@ __global__ void fill_bf16_kernel(uint16_t* p, size_t n, uint32_t seed) {
 
 std::string hb_tune_key(const hb_op_desc& d, int sm_count, int world) {
   char buf[160];
-  snprintf(buf, sizeof(buf), "%s %s %lld %lld %lld %d %d sm%d w%d",
+  (void)world;
+  snprintf(buf, sizeof(buf), "%s %s %lld %lld %lld %d %d sm%d",
            d.op == HB_OP_MATMUL ? "matmul" : "attention", d.dtype == HB_BF16 ? "bf16" : "f32",
-           (long long)d.m, (long long)d.n, (long long)d.k, d.layout, d.epilogue, sm_count, world);
+           (long long)d.m, (long long)d.n, (long long)d.k, d.layout, d.epilogue, sm_count);
   return buf;
 }
 

@@ -49,9 +49,10 @@ class Graph:
         return i.value
 
     # -- nodes --------------------------------------------------------------------
-    def _add(self, kind, ins, out, iparam=(), fparam=()):
+    def _add(self, kind, ins, out, iparam=(), fparam=(), stream=0):
         n = _capi.hb_node()
         n.kind = kind
+        n.stream = stream
         for k in range(4):
             n.inputs[k] = ins[k] if k < len(ins) and ins[k] is not None else -1
             n.iparam[k] = iparam[k] if k < len(iparam) else 0
@@ -69,8 +70,10 @@ class Graph:
             scale = float(self.meta[q][1][-1]) ** -0.5
         return self._add(NODE_ATTENTION, [q, k, v, lse], out, [int(causal)], [scale])
 
-    def all_reduce(self, x, algo=_capi.HB_AR_AUTO):
-        return self._add(NODE_ALL_REDUCE, [], x, [algo])
+    def all_reduce(self, x, algo=_capi.HB_AR_AUTO, stream=0):
+        """stream=1 puts the collective on the context's side stream so that it overlaps
+        the nodes that do not depend on it."""
+        return self._add(NODE_ALL_REDUCE, [], x, [algo], stream=stream)
 
     def rmsnorm(self, x, gain, out, residual=None, eps=1e-5):
         return self._add(NODE_RMSNORM, [x, gain, residual], out, [], [eps])

@@ -76,13 +76,17 @@ def _contig(shape) -> tuple:
 class Context:
     """One context per GPU (and per host thread or process)."""
 
-    def __init__(self, device: int = 0):
+    def __init__(self, device: int = 0, load_tune_cache: bool = True):
         h = C.c_void_p()
         st = _lib.hb_ctx_create(device, C.byref(h))
         if st != 0:
             raise HabuError(st, f"hb_ctx_create(device={device}) failed; an sm_100 GPU is required")
         self._h = h
         self.device = device
+        import os
+        cache = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tune_cache.txt")
+        if load_tune_cache and os.path.exists(cache):     # persisted autotune choices
+            self.tune_cache_load(cache)
 
     # -- plumbing ---------------------------------------------------------------
     def _check(self, st: int):

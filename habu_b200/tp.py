@@ -85,59 +85,78 @@ def shard_layer(full: Dict[str, np.ndarray], cfg: DecoderConfig, world: int, ran
 
 
 class DecoderGraph:
-    """Node list of the decoder forward for one rank; weights are bf16 bit patterns."""
+    """Node list of the decoder forward for one rank; weights are bf16 bit patterns.
+
+    With ``chunks > 1`` the batch is cut into that many micro-batches (whole sequences, so
+    attention stays local to a chunk).  Each chunk runs the same nodes on its own rows, and
+    the two allreduces of a chunk are put on the executor's side stream: while chunk c is
+    being summed over NVLink, the tensor cores work on chunk c+1.
+    """
 
     def __init__(self, ctx, cfg: DecoderConfig, world: int, rank: int, layers: List[Dict[str, np.ndarray]],
-                 algo: int = _capi.HB_AR_AUTO):
+                 algo: int = _capi.HB_AR_AUTO, chunks: int = 1):
         from .graph import Graph
         check_shardable(cfg, world)
-        self.ctx, self.cfg, self.world, self.rank = ctx, cfg, world, rank
+        if cfg.batch % chunks:
+            raise ValueError(f"batch {cfg.batch} does not split into {chunks} chunks")
+        self.ctx, self.cfg, self.world, self.rank, self.chunks = ctx, cfg, world, rank, chunks
         T, d, hd = cfg.tokens, cfg.d_model, cfg.head_dim
         ql, kl, fl = cfg.n_q_heads // world, cfg.n_kv_heads // world, cfg.ffn_hidden // world
         W = (ql + 2 * kl) * hd
+        Bc = cfg.batch // chunks            # sequences per chunk
+        Tc = Bc * cfg.seq                   # tokens per chunk
+        side = 1 if (chunks > 1 and world > 1) else 0
         g = self.graph = Graph(ctx)
         self.x0 = ctx.empty((T, d))
         self.out = ctx.empty((T, d))
         x0, out = g.input(self.x0), g.input(self.out)
+        rows = lambda t, c: g.view(t, c * Tc * d, (Tc, d), (d, 1))       # chunk c of a [T, d] tensor
         self.weights = []
-        x = None                       # residual stream (planner-owned after the first add)
-        pending = None                 # sublayer output not yet added into the stream
+        x = None                                  # residual stream [T, d], planner-owned after layer 0
+        pending = [None] * chunks                 # per chunk: sublayer output not yet added into the stream
         for li, lw in enumerate(layers):
             dev = {k: ctx.upload(v) for k, v in lw.items()}
             self.weights.append(dev)
             w = {k: g.input(v if k in ("g1", "g2") else v.T) for k, v in dev.items()}
-            # ---- attention sublayer
-            h = g.temp((T, d))
-            if x is None:
-                g.rmsnorm(x0, w["g1"], h, eps=cfg.eps)
-            else:
-                g.rmsnorm(pending, w["g1"], h, residual=x, eps=cfg.eps)
-            qkv = g.temp((T, W))
-            g.matmul(h, w["wqkv"], qkv)
-            g.rope(g.view(qkv, 0, (T, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
-            g.rope(g.view(qkv, ql * hd, (T, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
-            v4 = lambda off, H: g.view(qkv, off, (cfg.batch, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
-            attn = g.temp((T, ql * hd))
-            g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
-                        g.view(attn, 0, (cfg.batch, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)), causal=True)
-            ao = g.temp((T, d), symmetric=True)
-            g.matmul(attn, w["wo"], ao)
-            g.all_reduce(ao, algo)
-            # ---- FFN sublayer
-            h2 = g.temp((T, d))
-            if x is None:
+            first = x is None
+            if first:
                 x = g.temp((T, d))
-                g.add(x0, ao, x)
-                g.rmsnorm(x, w["g2"], h2, eps=cfg.eps)
-            else:
-                g.rmsnorm(ao, w["g2"], h2, residual=x, eps=cfg.eps)
-            act = g.temp((T, fl))
-            g.matmul(h2, w["wgu"], act, epilogue=_capi.HB_EPI_SWIGLU)
-            fo = g.temp((T, d), symmetric=True)
-            g.matmul(act, w["wd"], fo)
-            g.all_reduce(fo, algo)
-            pending = fo
-        g.add(x, pending, out)
+            # ---- attention sublayer, chunk by chunk
+            aos = []
+            for c in range(chunks):
+                h = g.temp((Tc, d))
+                if first:
+                    g.rmsnorm(rows(x0, c), w["g1"], h, eps=cfg.eps)
+                else:
+                    g.rmsnorm(pending[c], w["g1"], h, residual=rows(x, c), eps=cfg.eps)
+                qkv = g.temp((Tc, W))
+                g.matmul(h, w["wqkv"], qkv)
+                g.rope(g.view(qkv, 0, (Tc, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
+                g.rope(g.view(qkv, ql * hd, (Tc, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
+                v4 = lambda off, H: g.view(qkv, off, (Bc, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
+                attn = g.temp((Tc, ql * hd))
+                g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
+                            g.view(attn, 0, (Bc, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)), causal=True)
+                ao = g.temp((Tc, d), symmetric=True)
+                g.matmul(attn, w["wo"], ao)
+                g.all_reduce(ao, algo, stream=side)
+                aos.append(ao)
+            # ---- FFN sublayer, chunk by chunk
+            for c in range(chunks):
+                h2 = g.temp((Tc, d))
+                if first:
+                    g.add(rows(x0, c), aos[c], rows(x, c))
+                    g.rmsnorm(rows(x, c), w["g2"], h2, eps=cfg.eps)
+                else:
+                    g.rmsnorm(aos[c], w["g2"], h2, residual=rows(x, c), eps=cfg.eps)
+                act = g.temp((Tc, fl))
+                g.matmul(h2, w["wgu"], act, epilogue=_capi.HB_EPI_SWIGLU)
+                fo = g.temp((Tc, d), symmetric=True)
+                g.matmul(act, w["wd"], fo)
+                g.all_reduce(fo, algo, stream=side)
+                pending[c] = fo
+        for c in range(chunks):
+            g.add(rows(x, c), pending[c], rows(out, c))
         self.symmetric_needed = None
 
     def plan(self):

@@ -217,6 +217,8 @@ typedef struct hb_node {
   int32_t out;
   int32_t iparam[4];
   float fparam[2];
+  int32_t stream;          /* 0: the context's stream; 1: its side stream (runs concurrently;
+                              the executor orders conflicting nodes with events) */
 } hb_node;
 hb_status hb_graph_create(hb_ctx* ctx, hb_graph** out);
 hb_status hb_graph_destroy(hb_graph* g);

@@ -42,6 +42,13 @@ def test_single_gpu_forward_matches_oracle(ctx):
     # the planner reuses memory: the arena is smaller than the sum of all temporaries
     total = sum(int(l.split("bytes ")[1].split()[0]) for l in text.splitlines() if l.startswith("t"))
     assert arena < total
+    # micro-batched graph (2 chunks) computes the same values
+    dg2 = DecoderGraph(ctx, CFG, 1, 0, [_bits(shard_layer(l, CFG, 1, 0)) for l in layers], chunks=2)
+    dg2.plan()
+    ctx._check(model_ir._lib.hb_upload(ctx._h, dg2.x0.ptr, xb.ctypes.data_as(C.c_void_p), xb.nbytes))
+    dg2.run()
+    ctx.sync()
+    assert np.array_equal(oracle.from_bf16_bits(ctx.download(dg2.out)), got)
 
 
 def _tp_rank(rank, world):
@@ -61,28 +68,38 @@ def _tp_rank(rank, world):
     ref = decoder.forward(CFG, x0, layers, round_bf16=True)
     xb = oracle.to_bf16_bits(x0)
     outs = {}
-    for algo_name, algo in (("nccl", hb.HB_AR_NCCL), ("p2p", hb.HB_AR_AUTO)):
-        dg = DecoderGraph(ctx, CFG, world, rank, [_bits(shard_layer(l, CFG, world, rank)) for l in layers], algo)
+    cases = [("nccl", hb.HB_AR_NCCL, 1), ("p2p", hb.HB_AR_AUTO, 1), ("p2p-overlap", hb.HB_AR_AUTO, 2)]
+    graphs = {}
+    need = 0
+    for name, algo, chunks in cases:
+        dg = DecoderGraph(ctx, CFG, world, rank, [_bits(shard_layer(l, CFG, world, rank)) for l in layers], algo, chunks)
         _, sym = dg.plan()
-        if algo_name == "p2p":
-            ptr, handle = ctx.p2p_alloc(sym)
+        need = max(need, sym)
+        graphs[name] = dg
+    for name, algo, chunks in cases:
+        dg = graphs[name]
+        if name == "p2p":
+            ptr, handle = ctx.p2p_alloc(need)
             handles = [None] * world
             dist.all_gather_object(handles, handle)
-            ctx.p2p_attach(world, rank, handles, sym)
+            ctx.p2p_attach(world, rank, handles, need)
+        if name != "nccl":
             dg.plan()                       # re-plan: allreduce operands now live in the peer-mapped buffer
             assert "sym+" in dg.graph.describe()
         ctx._check(model_ir._lib.hb_upload(ctx._h, dg.x0.ptr, xb.ctypes.data_as(C.c_void_p), xb.nbytes))
         ctx.sync()
         dist.barrier()
-        dg.run()
+        for _ in range(2):
+            dg.run()
         ctx.sync()
         got = oracle.from_bf16_bits(ctx.download(dg.out))
-        assert bf16_close(got, ref) < 0, algo_name
-        outs[algo_name] = got
+        assert bf16_close(got, ref) < 0, name
+        outs[name] = got
         gathered = [None] * world
         dist.all_gather_object(gathered, got.tobytes())
         assert all(g == gathered[0] for g in gathered), "ranks disagree"
         dist.barrier()
+    assert np.array_equal(outs["p2p"], outs["p2p-overlap"]), "chunked overlap changed the result"
     ctx.close()
     dist.destroy_process_group()
 
