@@ -199,6 +199,40 @@ class AttentionWorkload:
                 f"{heads} of {self.B * self.H} (batch, head) pairs at seq {self.S} (oracle attention, fp32)")
 
 
+def attach_symmetric(ctx, rank, world, dist, nbytes):
+    """Gives the context a peer-mapped buffer of `nbytes` for its collectives and returns its
+    local address.  HB_COMM=nvls (default): torch's symmetric-memory allocator supplies the
+    buffer and its NVSwitch multicast mapping (plumbing only; the reduction kernels are the
+    library's); falls back to HB_COMM=p2p (the library's own cudaIpc mapping, no multicast)
+    when no multicast mapping is available."""
+    mode = os.environ.get("HB_COMM", "nvls")
+    if mode == "nvls":
+        try:
+            import torch
+            import torch.distributed._symmetric_memory as symm
+            payload = (nbytes + 255) // 256 * 256
+            buf = symm.empty(payload + ctx.p2p_flag_bytes(), dtype=torch.uint8, device=f"cuda:{torch.cuda.current_device()}")
+            buf.zero_()
+            hdl = symm.rendezvous(buf, dist.group.WORLD)
+            torch.cuda.synchronize()
+            dist.barrier()
+            if hdl.multicast_ptr:
+                ctx.p2p_attach_external(world, rank, list(hdl.buffer_ptrs), hdl.multicast_ptr, nbytes)
+                attach_symmetric.keep.append((buf, hdl))
+                return hdl.buffer_ptrs[rank], "nvls"
+        except Exception as e:   # plumbing unavailable: use the library's own mapping
+            if rank == 0:
+                print(f"symmetric-memory plumbing unavailable ({e}); using cudaIpc peer mapping", file=sys.stderr)
+    ptr, handle = ctx.p2p_alloc(nbytes)
+    handles = [None] * world
+    dist.all_gather_object(handles, handle)
+    ctx.p2p_attach(world, rank, handles, nbytes)
+    return ptr, "p2p"
+
+
+attach_symmetric.keep = []
+
+
 class DecoderWorkload:
     """Llama-style decoder block forward x2 layers, bf16, tensor-parallel over all ranks:
     d_model 4096, 32 query / 8 KV heads, head_dim 128, SwiGLU hidden 14336, batch 4 x seq 2048."""
@@ -231,17 +265,14 @@ class DecoderWorkload:
             layers.append({k: oracle.to_bf16_bits(v) for k, v in shard_layer(full, cfg, world, rank).items()})
             del full
         # micro-batches whose allreduce overlaps the next chunk's GEMMs (only useful with peers)
-        self.chunks = int(os.environ.get("HB_DECODER_CHUNKS", "4" if world > 1 else "1"))
+        self.chunks = int(os.environ.get("HB_DECODER_CHUNKS", "1"))
         self.dg = DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO, self.chunks)
         _, sym = self.dg.plan()
         if world > 1:
             ids = [ctx.comm_unique_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             ctx.comm_init_rank(world, rank, ids[0])
-            _, handle = ctx.p2p_alloc(sym)
-            handles = [None] * world
-            dist.all_gather_object(handles, handle)
-            ctx.p2p_attach(world, rank, handles, sym)
+            _, self.comm = attach_symmetric(ctx, rank, world, dist, sym)
             self.dg.plan()
         x0 = oracle.to_bf16_bits(decoder.make_input(cfg))
         self.hX = pinned(x0)
@@ -316,10 +347,7 @@ class MlpWorkload:
             dist.broadcast_object_list(ids, src=0)
             ctx.comm_init_rank(world, rank, ids[0])
             nbytes = MlpTrainer.grad_bytes(self.width, self.layers)
-            base, handle = ctx.p2p_alloc(nbytes)
-            handles = [None] * world
-            dist.all_gather_object(handles, handle)
-            ctx.p2p_attach(world, rank, handles, nbytes)
+            base, self.comm = attach_symmetric(ctx, rank, world, dist, nbytes)
         self.tr = MlpTrainer(ctx, self.width, self.batch, self.layers, ws, world=world, grads_base_ptr=base)
         del ws
         x, y = mlp.make_batch(self.batch, self.width, rank)
@@ -501,6 +529,8 @@ def main():
         roof["kernel_ms"] = kern_ms
         if sharded:
             roof["note"] = "whole-step figure: algorithmic flop of the block / (n_gpus x step time), all kernels and collectives included"
+        if hasattr(wl, "comm"):
+            roof["collective"] = wl.comm
         res = {"metric": wl.metric, "value": value, "unit": wl.unit, "ms_per_step": ms_per_step, "steps": steps,
                "scaling": getattr(wl, "scaling", "weak"), "workload": wl.desc, "l2": wl.flush_note, "roofline": roof,
                "gpu_launches": launches, "clocks": clocks}

@@ -7,7 +7,7 @@ The operator surface lives in :mod:`habu_b200.model_ir`, which loads
 or library fallback.  ``python -m habu_b200.build`` compiles the library in-tree.
 """
 _EXPORTS = ["Context", "HabuError", "Tensor", "matmul_configs", "HB_BF16", "HB_F32", "HB_I32", "HB_EPI_NONE",
-            "HB_EPI_GELU", "HB_EPI_SWIGLU", "HB_EPI_RESIDUAL", "HB_AR_AUTO", "HB_AR_NCCL", "HB_AR_P2P"]
+            "HB_EPI_GELU", "HB_EPI_SWIGLU", "HB_EPI_RESIDUAL", "HB_AR_AUTO", "HB_AR_NCCL", "HB_AR_P2P", "HB_AR_NVLS"]
 __all__ = list(_EXPORTS)
 
 

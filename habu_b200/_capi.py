@@ -17,7 +17,7 @@ STATUS_NAMES = ["OK", "Invalid", "Not_found", "Duplicate", "Cuda", "Nccl", "Time
                 "Unsupported", "No_memory"]
 HB_F32, HB_BF16, HB_I32 = 0, 1, 2
 HB_EPI_NONE, HB_EPI_GELU, HB_EPI_SWIGLU, HB_EPI_RESIDUAL = 0, 1, 2, 3
-HB_AR_AUTO, HB_AR_NCCL, HB_AR_P2P = 0, 1, 2
+HB_AR_AUTO, HB_AR_NCCL, HB_AR_P2P, HB_AR_NVLS = 0, 1, 2, 3
 HB_OP_MATMUL, HB_OP_ATTENTION = 0, 1
 HB_TUNE_CACHED, HB_TUNE_SEARCH = 0, 1
 HB_UNIQUE_ID_BYTES = 128
@@ -94,6 +94,7 @@ def load() -> C.CDLL:
         "hb_comm_destroy": [vp],
         "hb_p2p_alloc": [vp, C.c_size_t, C.POINTER(vp), vp],
         "hb_p2p_attach": [vp, i32, i32, vp, C.c_size_t],
+        "hb_p2p_attach_external": [vp, i32, i32, C.POINTER(vp), vp, C.c_size_t],
         "hb_all_reduce": [vp, vp, i64, i32, i32],
         "hb_graph_create": [vp, C.POINTER(vp)],
         "hb_graph_destroy": [vp],
@@ -119,6 +120,8 @@ def load() -> C.CDLL:
     lib.hb_last_error_string.restype = C.c_char_p
     lib.hb_static_last_error.argtypes = []
     lib.hb_static_last_error.restype = C.c_char_p
+    lib.hb_p2p_flag_bytes.argtypes = []
+    lib.hb_p2p_flag_bytes.restype = C.c_size_t
     lib.hb_launch_count.argtypes = [vp]
     lib.hb_launch_count.restype = i64
     lib.hb_sm_count.argtypes = [vp]

@@ -12,7 +12,12 @@
 //               release/acquire at system scope), so no CTA ever waits on another CTA of its
 //               own GPU.  Every wait is bounded: on time-out the kernel records
 //               HB_ERR_TIMEOUT and returns.  No multimem and no multicast loads are used.
-// Algorithmic bytes per rank: 2 * (world-1)/world * count * elem over NVLink.
+//   HB_AR_NVLS  the same two phases with the sum taken inside NVSwitch: each rank issues
+//               multimem.ld_reduce on the multicast mapping of its slice (the switch reads the
+//               slice from every GPU and returns the fp32-accumulated sum) and multimem.st
+//               broadcasts the result to every GPU.  Needs a multicast mapping of the
+//               symmetric buffer, supplied by the caller through hb_p2p_attach_external.
+// Algorithmic bytes per rank: 2 * (world-1)/world * count * elem over NVLink (P2P).
 #include <dlfcn.h>
 #include <nccl.h>
 #include <stdlib.h>
@@ -195,6 +200,51 @@ hb_allreduce_p2p_kernel(const ArParams p) {
   ar_barrier(p, 1, cta);
 }
 
+// ------------------------------------------------------------------ NVLS (in-switch) kernel
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_f32(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w) : "memory");
+}
+
+// `mc` is the multicast address of the payload.  Same slice ownership and the same
+// per-CTA handshakes as the P2P kernel; the element tail (count % N) goes through the
+// unicast peer pointers on rank 0.
+template <typename T>
+__global__ void __launch_bounds__(AR_THREADS, 4)
+hb_allreduce_nvls_kernel(const ArParams p, char* mc) {
+  constexpr int N = Vec<T>::N;
+  const int cta = blockIdx.x;
+  if (!ar_barrier(p, 0, cta)) return;
+  const int64_t nvec = p.count / N;
+  const int64_t per = (nvec + p.world - 1) / p.world;
+  const int64_t v0 = per * p.rank;
+  const int64_t v1 = min(nvec, v0 + per);
+  for (int64_t i = v0 + cta * (int64_t)AR_THREADS + threadIdx.x; i < v1; i += (int64_t)gridDim.x * AR_THREADS) {
+    char* a = mc + p.data_off + i * 16;
+    const uint4 v = sizeof(T) == 2 ? multimem_ld_reduce_bf16(a) : multimem_ld_reduce_f32(a);
+    multimem_st(a, v);
+  }
+  if (p.rank == 0 && cta == 0 && threadIdx.x < (int)(p.count % N)) {
+    const int64_t e = nvec * N + threadIdx.x;
+    float s = 0.f;
+    for (int r = 0; r < p.world; ++r) s += static_cast<float>(reinterpret_cast<const T*>(static_cast<char*>(p.peers[r]) + p.data_off)[e]);
+    for (int r = 0; r < p.world; ++r) reinterpret_cast<T*>(static_cast<char*>(p.peers[r]) + p.data_off)[e] = static_cast<T>(s);
+  }
+  ar_barrier(p, 1, cta);
+}
+
 }  // namespace
 
 extern "C" hb_status hb_comm_unique_id(void* id_out) {
@@ -239,10 +289,15 @@ extern "C" hb_status hb_comm_destroy(hb_ctx* ctx) {
     ctx->nccl_comm = nullptr;
   }
   hb_p2p_state& s = ctx->p2p;
-  for (int r = 0; r < (int)s.peers.size(); ++r)
-    if (r != s.rank && s.peers[r]) cudaIpcCloseMemHandle(s.peers[r]);
+  if (!s.external) {
+    for (int r = 0; r < (int)s.peers.size(); ++r)
+      if (r != s.rank && s.peers[r]) cudaIpcCloseMemHandle(s.peers[r]);
+    if (s.local) cudaFree(s.local);
+  }
   s.peers.clear();
-  if (s.local) { cudaFree(s.local); s.local = nullptr; }
+  s.local = nullptr;
+  s.multicast = nullptr;
+  s.external = false;
   s.world = 0;
   return HB_OK;
 }
@@ -301,6 +356,38 @@ extern "C" hb_status hb_p2p_attach(hb_ctx* ctx, int32_t world, int32_t rank, con
   return HB_OK;
 }
 
+extern "C" size_t hb_p2p_flag_bytes(void) { return AR_FLAG_BYTES; }
+
+// Registers a symmetric buffer the caller allocated and mapped: peer_ptrs[r] is rank r's
+// buffer as seen from this process (peer_ptrs[rank] the local one), `multicast_ptr` the
+// NVSwitch multicast mapping of the same buffer or NULL.  Each buffer must hold `bytes`
+// of payload (rounded up to 256) followed by hb_p2p_flag_bytes() of zeroed flag words.
+extern "C" hb_status hb_p2p_attach_external(hb_ctx* ctx, int32_t world, int32_t rank, const void* const* peer_ptrs,
+                                            void* multicast_ptr, size_t bytes) {
+  if (!ctx || !peer_ptrs) return HB_ERR_INVALID;
+  hb_p2p_state& s = ctx->p2p;
+  if (s.local) return hb_fail(ctx, HB_ERR_DUPLICATE, "p2p: this context already has a symmetric buffer");
+  if (world < 2 || world > AR_MAX_WORLD || rank < 0 || rank >= world)
+    return hb_fail(ctx, HB_ERR_INVALID, "p2p: rank %d of %d (2..%d ranks)", rank, world, AR_MAX_WORLD);
+  if (bytes == 0) return hb_fail(ctx, HB_ERR_INVALID, "p2p: empty buffer");
+  for (int r = 0; r < world; ++r)
+    if (!peer_ptrs[r] || (reinterpret_cast<uintptr_t>(peer_ptrs[r]) & 15))
+      return hb_fail(ctx, HB_ERR_INVALID, "p2p: peer pointer %d is null or misaligned", r);
+  if (reinterpret_cast<uintptr_t>(multicast_ptr) & 15) return hb_fail(ctx, HB_ERR_INVALID, "p2p: misaligned multicast pointer");
+  s.peers.assign(world, nullptr);
+  for (int r = 0; r < world; ++r) s.peers[r] = const_cast<void*>(peer_ptrs[r]);
+  s.local = s.peers[rank];
+  s.multicast = multicast_ptr;
+  s.external = true;
+  s.bytes = (bytes + 255) & ~size_t(255);
+  s.world = world;
+  s.rank = rank;
+  s.epoch = 0;
+  ctx->world = world;
+  ctx->rank = rank;
+  return HB_OK;
+}
+
 extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo) {
   if (!ctx) return HB_ERR_INVALID;
   if (!data) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: null pointer");
@@ -312,7 +399,7 @@ extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32
   const char* lo = static_cast<const char*>(s.local);
   const bool inside = s.world > 1 && static_cast<const char*>(data) >= lo &&
                       static_cast<const char*>(data) + (size_t)count * es <= lo + s.bytes;
-  if (algo == HB_AR_AUTO) algo = inside ? HB_AR_P2P : HB_AR_NCCL;
+  if (algo == HB_AR_AUTO) algo = inside ? (s.multicast ? HB_AR_NVLS : HB_AR_P2P) : HB_AR_NCCL;
   if (algo == HB_AR_NCCL) {
     NcclApi* api = nccl_api();
     if (!api || !ctx->nccl_comm) return hb_fail(ctx, HB_ERR_NCCL, "all_reduce: no NCCL communicator (hb_comm_init_rank)");
@@ -323,7 +410,9 @@ extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32
     ctx->launches++;
     return HB_OK;
   }
-  if (algo != HB_AR_P2P) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: unknown algorithm %d", algo);
+  if (algo != HB_AR_P2P && algo != HB_AR_NVLS) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: unknown algorithm %d", algo);
+  if (algo == HB_AR_NVLS && !s.multicast)
+    return hb_fail(ctx, HB_ERR_NOT_FOUND, "all_reduce: no multicast mapping attached (hb_p2p_attach_external)");
   if (s.world < 2) return hb_fail(ctx, HB_ERR_NOT_FOUND, "all_reduce: no peer buffers attached (hb_p2p_attach)");
   if (!inside)
     return hb_fail(ctx, HB_ERR_INVALID, "all_reduce: P2P needs the tensor inside the symmetric buffer of hb_p2p_alloc");
@@ -349,7 +438,11 @@ extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32
   }
   if (grid > cap) grid = cap;
 #define HB_AR_LAUNCH(T, W) hb_allreduce_p2p_kernel<T, W><<<grid, AR_THREADS, 0, ctx->stream>>>(p)
-  if (dtype == HB_BF16) {
+  if (algo == HB_AR_NVLS) {
+    char* mc = static_cast<char*>(s.multicast);
+    if (dtype == HB_BF16) hb_allreduce_nvls_kernel<__nv_bfloat16><<<grid, AR_THREADS, 0, ctx->stream>>>(p, mc);
+    else hb_allreduce_nvls_kernel<float><<<grid, AR_THREADS, 0, ctx->stream>>>(p, mc);
+  } else if (dtype == HB_BF16) {
     if (s.world == 2) HB_AR_LAUNCH(__nv_bfloat16, 2);
     else if (s.world <= 4) HB_AR_LAUNCH(__nv_bfloat16, 4);
     else HB_AR_LAUNCH(__nv_bfloat16, 8);

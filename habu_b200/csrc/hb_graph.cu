@@ -324,7 +324,11 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
     g->last_side_node = -1;
     if (any_side) {
       if (!ctx->side_stream) {
-        cudaError_t e = cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking);
+        // highest priority: when SM resources free up, the collective's CTAs are placed before
+        // the queued compute kernels', so it starts as soon as its producer finishes
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        cudaError_t e = cudaStreamCreateWithPriority(&ctx->side_stream, cudaStreamNonBlocking, hi);
         if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaStreamCreate(side)");
       }
       for (int i = 0; i < nn; ++i) {

@@ -32,6 +32,8 @@ struct hb_p2p_state {
   void* local = nullptr;              // this rank's symmetric buffer (data + flags)
   std::vector<void*> peers;           // mapped base pointers, peers[rank] == local
   void** d_peers = nullptr;           // device copy of `peers`
+  void* multicast = nullptr;          // NVSwitch multicast mapping of the same buffer (optional)
+  bool external = false;              // buffer and mappings are owned by the caller
   uint32_t epoch = 0;
 };
 

@@ -19,7 +19,7 @@ from typing import Optional, Sequence
 import numpy as np
 
 from . import _capi
-from ._capi import (HB_AR_AUTO, HB_AR_NCCL, HB_AR_P2P, HB_BF16, HB_EPI_GELU, HB_EPI_NONE,
+from ._capi import (HB_AR_AUTO, HB_AR_NCCL, HB_AR_NVLS, HB_AR_P2P, HB_BF16, HB_EPI_GELU, HB_EPI_NONE,
                     HB_EPI_RESIDUAL, HB_EPI_SWIGLU, HB_F32, HB_I32, HB_OP_MATMUL,
                     HB_TUNE_CACHED, HB_TUNE_SEARCH)
 
@@ -289,6 +289,16 @@ class Context:
 
     def p2p_attach(self, world: int, rank: int, handles: Sequence[bytes], nbytes: int):
         self._check(_lib.hb_p2p_attach(self._h, world, rank, b"".join(handles), nbytes))
+
+    @staticmethod
+    def p2p_flag_bytes() -> int:
+        return int(_lib.hb_p2p_flag_bytes())
+
+    def p2p_attach_external(self, world: int, rank: int, peer_ptrs: Sequence[int], multicast_ptr: Optional[int],
+                            nbytes: int):
+        """Register a caller-owned symmetric buffer (and its multicast mapping, if any)."""
+        arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
+        self._check(_lib.hb_p2p_attach_external(self._h, world, rank, arr, C.c_void_p(multicast_ptr or 0), nbytes))
 
     def all_reduce(self, x: Tensor, algo: int = HB_AR_AUTO) -> Tensor:
         n = 1

@@ -177,7 +177,7 @@ hb_status hb_argmax(hb_ctx* ctx, const void* x, int32_t* out, int64_t rows, int6
  * communicator bound to `ctx`.  HB_AR_NCCL enqueues ncclAllReduce on the stream;
  * HB_AR_P2P runs this library's two-shot kernel over peer-mapped buffers (plain peer
  * loads and stores, bounded flag waits). No reference counterpart. */
-enum { HB_AR_AUTO = 0, HB_AR_NCCL = 1, HB_AR_P2P = 2 };
+enum { HB_AR_AUTO = 0, HB_AR_NCCL = 1, HB_AR_P2P = 2, HB_AR_NVLS = 3 };
 #define HB_UNIQUE_ID_BYTES 128
 #define HB_IPC_HANDLE_BYTES 64
 hb_status hb_comm_unique_id(void* id_out /* HB_UNIQUE_ID_BYTES */);
@@ -188,6 +188,13 @@ hb_status hb_comm_destroy(hb_ctx* ctx);
 hb_status hb_p2p_alloc(hb_ctx* ctx, size_t bytes, void** dev_ptr, void* handle_out);
 hb_status hb_p2p_attach(hb_ctx* ctx, int32_t world, int32_t rank, const void* all_handles,
                         size_t bytes);
+/* Alternative to hb_p2p_alloc/attach for callers that already own a symmetric buffer
+ * (and, optionally, its NVSwitch multicast mapping, which enables HB_AR_NVLS: the sum is
+ * taken inside the switch with multimem.ld_reduce / multimem.st).  Each rank's buffer holds
+ * `bytes` of payload, rounded up to 256, followed by hb_p2p_flag_bytes() zeroed bytes. */
+size_t hb_p2p_flag_bytes(void);
+hb_status hb_p2p_attach_external(hb_ctx* ctx, int32_t world, int32_t rank,
+                                 const void* const* peer_ptrs, void* multicast_ptr, size_t bytes);
 hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo);
 
 /* ---- model-IR executor: node list, memory planner, launcher --------------------------

@@ -84,3 +84,68 @@ def test_single_rank_all_reduce_is_identity(ctx):
     d = ctx.upload(x)
     ctx.all_reduce(d)
     assert np.array_equal(ctx.download(d), x)
+
+
+def _nvls_rank(rank, world, count, dtype_name):
+    """In-switch reduction over a multicast mapping.  The symmetric buffer and its multicast
+    mapping come from torch's symmetric-memory allocator (plumbing only); the reduction is
+    this library's multimem kernel."""
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm
+
+    import habu_b200 as hb
+    import oracle
+    from habu_b200 import model_ir
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    ctx = hb.Context(rank)
+    es = 2 if dtype_name == "bf16" else 4
+    payload = (count * es + 255) // 256 * 256
+    buf = symm.empty(payload + hb.Context.p2p_flag_bytes(), dtype=torch.uint8, device=f"cuda:{rank}")
+    buf.zero_()
+    hdl = symm.rendezvous(buf, dist.group.WORLD)
+    torch.cuda.synchronize()
+    dist.barrier()
+    if not hdl.multicast_ptr:
+        if rank == 0:
+            print("no multicast support on this box: NVLS path not exercised")
+        dist.destroy_process_group()
+        return
+    ctx.p2p_attach_external(world, rank, list(hdl.buffer_ptrs), hdl.multicast_ptr, count * es)
+    dtype = hb.HB_BF16 if dtype_name == "bf16" else hb.HB_F32
+    per_rank = [oracle.normal((count,), 700 + r) for r in range(world)]
+    if dtype_name == "bf16":
+        per_rank = [oracle.round_bf16(x) for x in per_rank]
+    host = oracle.to_bf16_bits(per_rank[rank]) if dtype_name == "bf16" else per_rank[rank]
+    x = ctx.wrap(hdl.buffer_ptrs[rank], (count,), dtype)
+    ref = per_rank[0].astype(np.float32).copy()
+    for r in range(1, world):
+        ref = ref + per_rank[r]
+    for algo in (hb.HB_AR_NVLS, hb.HB_AR_P2P, hb.HB_AR_AUTO):
+        ctx._check(model_ir._lib.hb_upload(ctx._h, x.ptr, host.ctypes.data_as(C.c_void_p), host.nbytes))
+        ctx.sync()
+        dist.barrier()
+        ctx.all_reduce(x, algo)
+        ctx.sync()
+        got = ctx.download(x)
+        got = oracle.from_bf16_bits(got) if dtype_name == "bf16" else got
+        tol = 2.0 ** -7 * np.maximum(np.abs(ref), 1.0) if dtype_name == "bf16" else 1e-5 * np.maximum(np.abs(ref), 1.0)
+        assert np.all(np.abs(got - ref) <= tol), (algo, float(np.abs(got - ref).max()))
+        gathered = [None] * world
+        dist.all_gather_object(gathered, got.tobytes())
+        assert all(g == gathered[0] for g in gathered), "ranks disagree"
+        dist.barrier()
+    ctx.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("count,dtype", [(1 << 20, "bf16"), (100003, "bf16"), (4099, "f32")])
+def test_in_switch_all_reduce_over_multicast(count, dtype):
+    n = _gpu_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    from mp_util import run_ranks
+    run_ranks(_nvls_rank, min(n, 4) if n >= 4 else 2, (count, dtype))
