@@ -266,7 +266,9 @@ class DecoderWorkload:
             del full
         # micro-batches whose allreduce overlaps the next chunk's GEMMs (only useful with peers)
         self.chunks = int(os.environ.get("HB_DECODER_CHUNKS", "1"))
-        self.dg = DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO, self.chunks)
+        # fused reduce-scatter + residual + RMSNorm + all-gather nodes instead of allreduce + replicated norms
+        self.fused = os.environ.get("HB_DECODER_FUSED", "1") == "1" and world > 1 and self.chunks == 1
+        self.dg = DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO, self.chunks, fused=self.fused)
         _, sym = self.dg.plan()
         if world > 1:
             ids = [ctx.comm_unique_id() if rank == 0 else None]

@@ -455,3 +455,184 @@ extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "all_reduce launch");
 }
+
+// ---------------------------------------------------------------------------------------
+// Fused collective + glue: reduce-scatter -> residual add -> RMSNorm -> all-gather.
+//
+// After a row-parallel GEMM every rank holds a partial [rows, cols] product.  Instead of
+// an allreduce followed by a replicated residual add and RMSNorm on all `rows`, each rank
+// owns rows/world rows: it sums the partials of its rows (multimem.ld_reduce through the
+// switch, or plain loads from every peer), adds them into its shard of the residual
+// stream, normalises, and publishes only the normalised rows to every rank (multimem.st or
+// plain peer stores).  NVLink carries the same bytes as the allreduce; the replicated
+// elementwise passes disappear and the residual stream stays sharded by rows.
+//   mode 0: out[row] = rmsnorm(residual_out[row]) * gain        (published to all ranks)
+//   mode 1: out[row] = residual_out[row]                        (final gather of the stream)
+// with residual_out[row] = bf16(residual_in[row] + bf16(sum of partials[row])).
+// One CTA per row at a time (256 threads, the row in registers), persistent over the
+// rank's rows; same per-CTA handshakes and bounded waits as the allreduce kernels.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr int ARN_MAX_VEC = 8;   // cols <= 256 * 8 * 8 = 16384
+
+struct ArnParams {
+  ArParams ar;                 // peers, flag block, world/rank, epoch (data_off = partial's offset)
+  size_t out_off;              // byte offset of `out` inside the symmetric buffers
+  char* mc;                    // multicast base or null
+  const uint4* gain;
+  const uint4* residual_in;    // local [rows, cols] (only this rank's rows are read)
+  uint4* residual_out;         // local [rows, cols] (only this rank's rows are written)
+  int rows, cols8;
+  float inv_cols, eps;
+  int mode;
+};
+
+template <bool NVLS, int WORLD>
+__global__ void __launch_bounds__(AR_THREADS, 2)
+hb_allreduce_norm_kernel(const ArnParams p) {
+  __shared__ float red[AR_THREADS / 32];
+  const int cta = blockIdx.x;
+  if (!ar_barrier(p.ar, 0, cta)) return;
+  const int per = p.rows / p.ar.world;
+  const int row0 = per * p.ar.rank;
+  for (int row = row0 + cta; row < row0 + per; row += gridDim.x) {
+    const int64_t base = static_cast<int64_t>(row) * p.cols8;
+    float v[ARN_MAX_VEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < ARN_MAX_VEC; ++k) {
+      const int c = threadIdx.x + k * AR_THREADS;
+      if (c < p.cols8) {
+        uint4 s4;
+        if (NVLS) {
+          s4 = multimem_ld_reduce_bf16(p.mc + p.ar.data_off + (base + c) * 16);
+        } else {
+          uint4 pv[WORLD];
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r)
+            if (r < p.ar.world)
+              pv[r] = *(reinterpret_cast<const uint4*>(static_cast<const char*>(p.ar.peers[r]) + p.ar.data_off) + base + c);
+          float acc[8] = {};
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r)
+            if (r < p.ar.world) Vec<__nv_bfloat16>::add(acc, pv[r]);
+          s4 = Vec<__nv_bfloat16>::pack(acc);
+        }
+        const uint4 r4 = p.residual_in[base + c];
+        const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w}, rw[4] = {r4.x, r4.y, r4.z, r4.w};
+        uint32_t xw[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&sw[j]));
+          const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[j]));
+          __nv_bfloat162 x = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+          xw[j] = *reinterpret_cast<uint32_t*>(&x);
+          const float2 xf = __bfloat1622float2(x);
+          v[k][2 * j] = xf.x;
+          v[k][2 * j + 1] = xf.y;
+          ss += xf.x * xf.x + xf.y * xf.y;
+        }
+        p.residual_out[base + c] = make_uint4(xw[0], xw[1], xw[2], xw[3]);
+      }
+    }
+    float inv = 1.0f;
+    if (p.mode == 0) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      __syncthreads();                         // red[] from the previous row has been read
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < AR_THREADS / 32; ++w) tot += red[w];
+      inv = rsqrtf(tot * p.inv_cols + p.eps);
+    }
+#pragma unroll
+    for (int k = 0; k < ARN_MAX_VEC; ++k) {
+      const int c = threadIdx.x + k * AR_THREADS;
+      if (c < p.cols8) {
+        uint32_t o[4];
+        if (p.mode == 0) {
+          const uint4 g = __ldg(p.gain + c);
+          const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[j]));
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[k][2 * j] * inv * gf.x, v[k][2 * j + 1] * inv * gf.y);
+            o[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[k][2 * j], v[k][2 * j + 1]);
+            o[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        const uint4 o4 = make_uint4(o[0], o[1], o[2], o[3]);
+        if (NVLS) {
+          multimem_st(p.mc + p.out_off + (base + c) * 16, o4);
+        } else {
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r)
+            if (r < p.ar.world) *(reinterpret_cast<uint4*>(static_cast<char*>(p.ar.peers[r]) + p.out_off) + base + c) = o4;
+        }
+      }
+    }
+  }
+  ar_barrier(p.ar, 1, cta);
+}
+
+}  // namespace
+
+extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const void* gain, const void* residual_in,
+                                        void* residual_out, void* out, int64_t rows, int64_t cols, float eps,
+                                        int32_t mode, int32_t algo) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!partial || !residual_in || !residual_out || !out || (mode == 0 && !gain))
+    return hb_fail(ctx, HB_ERR_INVALID, "all_reduce_norm: null pointer");
+  if (mode != 0 && mode != 1) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce_norm: unknown mode %d", mode);
+  hb_p2p_state& s = ctx->p2p;
+  if (s.world < 2) return hb_fail(ctx, HB_ERR_NOT_FOUND, "all_reduce_norm: no peer buffers attached");
+  if (rows <= 0 || cols <= 0 || rows % s.world) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce_norm: rows must split evenly over the ranks");
+  if (cols % 8 || cols > AR_THREADS * ARN_MAX_VEC * 8) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "all_reduce_norm: cols must be a multiple of 8, at most %d", AR_THREADS * ARN_MAX_VEC * 8);
+  const char* lo = static_cast<const char*>(s.local);
+  const size_t nbytes = (size_t)rows * cols * 2;
+  auto inside = [&](const void* p) { return static_cast<const char*>(p) >= lo && static_cast<const char*>(p) + nbytes <= lo + s.bytes; };
+  if (!inside(partial) || !inside(out)) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce_norm: partial and out must lie in the symmetric buffer");
+  if ((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(gain) |
+       reinterpret_cast<uintptr_t>(residual_in) | reinterpret_cast<uintptr_t>(residual_out)) & 15)
+    return hb_fail(ctx, HB_ERR_INVALID, "all_reduce_norm: pointers must be 16-byte aligned");
+  if (algo == HB_AR_AUTO) algo = s.multicast ? HB_AR_NVLS : HB_AR_P2P;
+  if (algo == HB_AR_NVLS && !s.multicast) return hb_fail(ctx, HB_ERR_NOT_FOUND, "all_reduce_norm: no multicast mapping attached");
+  if (algo != HB_AR_NVLS && algo != HB_AR_P2P) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "all_reduce_norm: algorithm %d", algo);
+  ArnParams p;
+  memset(&p, 0, sizeof(p));
+  for (int r = 0; r < s.world; ++r) p.ar.peers[r] = s.peers[r];
+  p.ar.flag_off = s.bytes;
+  p.ar.data_off = static_cast<const char*>(partial) - lo;
+  p.ar.count = rows * cols;
+  p.ar.world = s.world;
+  p.ar.rank = s.rank;
+  p.ar.epoch = ++s.epoch;
+  p.ar.status = ctx->d_status;
+  p.out_off = static_cast<const char*>(out) - lo;
+  p.mc = static_cast<char*>(s.multicast);
+  p.gain = static_cast<const uint4*>(gain);
+  p.residual_in = static_cast<const uint4*>(residual_in);
+  p.residual_out = static_cast<uint4*>(residual_out);
+  p.rows = (int)rows;
+  p.cols8 = (int)(cols / 8);
+  p.inv_cols = 1.0f / (float)cols;
+  p.eps = eps;
+  p.mode = mode;
+  int grid = (int)(rows / s.world);
+  int cap = ctx->sm_count * 2 < AR_MAX_CTAS ? ctx->sm_count * 2 : AR_MAX_CTAS;
+  if (grid > cap) grid = cap;
+  if (algo == HB_AR_NVLS) hb_allreduce_norm_kernel<true, 1><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+  else if (s.world == 2) hb_allreduce_norm_kernel<false, 2><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+  else if (s.world <= 4) hb_allreduce_norm_kernel<false, 4><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+  else hb_allreduce_norm_kernel<false, 8><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "all_reduce_norm launch");
+}

@@ -52,7 +52,7 @@ struct hb_graph {
 namespace {
 
 const char* kNodeNames[] = {"matmul", "attention", "all_reduce", "rmsnorm", "rope", "embedding",
-                            "swiglu", "gelu", "add", "argmax"};
+                            "swiglu", "gelu", "add", "argmax", "all_reduce_norm"};
 size_t elem_size(int dtype) { return dtype == HB_BF16 ? 2 : 4; }
 
 int root_of(const hb_graph* g, int id) {
@@ -182,8 +182,8 @@ extern "C" hb_status hb_graph_view(hb_graph* g, int32_t base, int64_t offset, in
 
 extern "C" hb_status hb_graph_add(hb_graph* g, const hb_node* n) {
   if (!g || !n) return HB_ERR_INVALID;
-  if (n->kind < 0 || n->kind > HB_NODE_ARGMAX) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: unknown node kind %d", n->kind);
-  static const int n_in[] = {2, 3, 0, 2, 0, 2, 1, 1, 2, 1};   // required inputs per kind
+  if (n->kind < 0 || n->kind > HB_NODE_AR_NORM) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: unknown node kind %d", n->kind);
+  static const int n_in[] = {2, 3, 0, 2, 0, 2, 1, 1, 2, 1, 1};   // required leading inputs per kind
   for (int i = 0; i < 4; ++i) {
     if (i < n_in[n->kind] && !valid_id(g, n->in[i]))
       return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: %s node input %d names unknown tensor %d", kNodeNames[n->kind], i, n->in[i]);
@@ -216,10 +216,13 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
     const hb_node& n = g->nodes[i];
     for (int k = 0; k < 4; ++k) {
       if (n.in[k] < 0) continue;
+      if (n.kind == HB_NODE_AR_NORM && k == 3) continue;   // residual_out is written, not read
       const int r = root_of(g, n.in[k]);
       if (g->tensors[r].kind != 1) continue;
       bool written = false;
-      for (int j = 0; j < i && !written; ++j) written = root_of(g, g->nodes[j].out) == r;
+      for (int j = 0; j < i && !written; ++j)
+        written = root_of(g, g->nodes[j].out) == r ||
+                  (g->nodes[j].kind == HB_NODE_AR_NORM && g->nodes[j].in[3] >= 0 && root_of(g, g->nodes[j].in[3]) == r);
       const bool inout = (n.kind == HB_NODE_ROPE || n.kind == HB_NODE_ALL_REDUCE) && root_of(g, n.out) == r;
       if (!written && !inout)
         return hb_fail(ctx, HB_ERR_INVALID, "graph: node %d (%s) reads planner-owned tensor %d before any node writes it", i,
@@ -316,7 +319,8 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
       const hb_node& n = g->nodes[i];
       if (n.stream != 0) any_side = true;
       for (int k = 0; k < 4; ++k)
-        if (n.in[k] >= 0) foot[i].push_back(range_of(n.in[k], n.kind == HB_NODE_RMSNORM && k == 2));
+        if (n.in[k] >= 0)
+          foot[i].push_back(range_of(n.in[k], (n.kind == HB_NODE_RMSNORM && k == 2) || (n.kind == HB_NODE_AR_NORM && k == 3)));
       foot[i].push_back(range_of(n.out, true));
     }
     g->wait_for.assign(nn, -1);
@@ -418,6 +422,16 @@ static hb_status run_node(hb_graph* g, int i) {
       case HB_NODE_ADD:
         st = hb_add(ctx, T(n.in[0]).ptr, T(n.in[1]).ptr, T(n.out).ptr, numel(T(n.in[0])));
         break;
+      case HB_NODE_AR_NORM: {
+        const hb_graph_tensor& x = T(n.in[0]);
+        if (x.rank != 2 || !is_contiguous(x) || !is_contiguous(T(n.out)) || n.in[2] < 0 || n.in[3] < 0) {
+          st = hb_fail(ctx, HB_ERR_INVALID, "graph: all_reduce_norm needs contiguous [rows, cols], a residual input and a residual output");
+          break;
+        }
+        st = hb_all_reduce_norm(ctx, x.ptr, n.in[1] >= 0 ? T(n.in[1]).ptr : nullptr, T(n.in[2]).ptr, T(n.in[3]).ptr, T(n.out).ptr,
+                                x.shape[0], x.shape[1], n.fparam[0], n.iparam[0], n.iparam[1]);
+        break;
+      }
       case HB_NODE_ARGMAX: {
         const hb_graph_tensor& x = T(n.in[0]);
         st = hb_argmax(ctx, x.ptr, static_cast<int32_t*>(T(n.out).ptr), x.shape[0], x.shape[1]);

@@ -9,7 +9,7 @@ from . import _capi
 from .model_ir import Context, Tensor, _contig, _lib
 
 (NODE_MATMUL, NODE_ATTENTION, NODE_ALL_REDUCE, NODE_RMSNORM, NODE_ROPE, NODE_EMBEDDING, NODE_SWIGLU, NODE_GELU,
- NODE_ADD, NODE_ARGMAX) = range(10)
+ NODE_ADD, NODE_ARGMAX, NODE_AR_NORM) = range(11)
 T_SYMMETRIC = 1
 
 
@@ -74,6 +74,12 @@ class Graph:
         """stream=1 puts the collective on the context's side stream so that it overlaps
         the nodes that do not depend on it."""
         return self._add(NODE_ALL_REDUCE, [], x, [algo], stream=stream)
+
+    def all_reduce_norm(self, partial, gain, residual_in, residual_out, out, eps=1e-5, gather_only=False,
+                        algo=_capi.HB_AR_AUTO):
+        """Fused reduce-scatter + residual add + RMSNorm + all-gather (gather_only: publish the
+        updated residual rows instead of their norm)."""
+        return self._add(NODE_AR_NORM, [partial, gain, residual_in, residual_out], out, [int(gather_only), algo], [eps])
 
     def rmsnorm(self, x, gain, out, residual=None, eps=1e-5):
         return self._add(NODE_RMSNORM, [x, gain, residual], out, [], [eps])

@@ -94,9 +94,13 @@ class DecoderGraph:
     """
 
     def __init__(self, ctx, cfg: DecoderConfig, world: int, rank: int, layers: List[Dict[str, np.ndarray]],
-                 algo: int = _capi.HB_AR_AUTO, chunks: int = 1):
+                 algo: int = _capi.HB_AR_AUTO, chunks: int = 1, fused: bool = False):
         from .graph import Graph
         check_shardable(cfg, world)
+        self._out_id = None
+        if fused and world > 1 and chunks == 1:
+            self._build_fused(ctx, cfg, world, rank, layers, algo)
+            return
         if cfg.batch % chunks:
             raise ValueError(f"batch {cfg.batch} does not split into {chunks} chunks")
         self.ctx, self.cfg, self.world, self.rank, self.chunks = ctx, cfg, world, rank, chunks
@@ -108,8 +112,8 @@ class DecoderGraph:
         side = 1 if (chunks > 1 and world > 1) else 0
         g = self.graph = Graph(ctx)
         self.x0 = ctx.empty((T, d))
-        self.out = ctx.empty((T, d))
-        x0, out = g.input(self.x0), g.input(self.out)
+        self._out = ctx.empty((T, d))
+        x0, out = g.input(self.x0), g.input(self._out)
         rows = lambda t, c: g.view(t, c * Tc * d, (Tc, d), (d, 1))       # chunk c of a [T, d] tensor
         self.weights = []
         x = None                                  # residual stream [T, d], planner-owned after layer 0
@@ -158,6 +162,58 @@ class DecoderGraph:
         for c in range(chunks):
             g.add(rows(x, c), pending[c], rows(out, c))
         self.symmetric_needed = None
+
+    def _build_fused(self, ctx, cfg, world, rank, layers, algo):
+        """Sequence-parallel form: each allreduce + residual add + RMSNorm becomes one fused
+        node (reduce-scatter, add and norm on this rank's rows, all-gather of the normalised
+        rows); the residual stream is sharded by rows and gathered once at the end."""
+        from .graph import Graph
+        if cfg.tokens % world:
+            raise ValueError("tokens must split evenly over the ranks")
+        self.ctx, self.cfg, self.world, self.rank, self.chunks = ctx, cfg, world, rank, 1
+        T, d, hd = cfg.tokens, cfg.d_model, cfg.head_dim
+        ql, kl, fl = cfg.n_q_heads // world, cfg.n_kv_heads // world, cfg.ffn_hidden // world
+        W = (ql + 2 * kl) * hd
+        g = self.graph = Graph(ctx)
+        self.x0 = ctx.empty((T, d))
+        x0 = g.input(self.x0)
+        self.weights = [{k: ctx.upload(v) for k, v in lw.items()} for lw in layers]
+        ws = [{k: g.input(v if k in ("g1", "g2") else v.T) for k, v in dev.items()} for dev in self.weights]
+        x = g.temp((T, d))                          # residual stream: only this rank's rows are live
+        h = g.temp((T, d))
+        g.rmsnorm(x0, ws[0]["g1"], h, eps=cfg.eps)
+        for li, w in enumerate(ws):
+            qkv = g.temp((T, W))
+            g.matmul(h, w["wqkv"], qkv)
+            g.rope(g.view(qkv, 0, (T, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
+            g.rope(g.view(qkv, ql * hd, (T, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
+            v4 = lambda off, H: g.view(qkv, off, (cfg.batch, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
+            attn = g.temp((T, ql * hd))
+            g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
+                        g.view(attn, 0, (cfg.batch, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)), causal=True)
+            ao = g.temp((T, d), symmetric=True)
+            g.matmul(attn, w["wo"], ao)
+            h2 = g.temp((T, d), symmetric=True)
+            g.all_reduce_norm(ao, w["g2"], x0 if li == 0 else x, x, h2, eps=cfg.eps, algo=algo)
+            act = g.temp((T, fl))
+            g.matmul(h2, w["wgu"], act, epilogue=_capi.HB_EPI_SWIGLU)
+            fo = g.temp((T, d), symmetric=True)
+            g.matmul(act, w["wd"], fo)
+            nxt = g.temp((T, d), symmetric=True)
+            if li + 1 < len(ws):
+                g.all_reduce_norm(fo, ws[li + 1]["g1"], x, x, nxt, eps=cfg.eps, algo=algo)
+                h = nxt
+            else:
+                g.all_reduce_norm(fo, None, x, x, nxt, gather_only=True, algo=algo)
+                self._out_id = nxt
+        self.symmetric_needed = None
+
+    @property
+    def out(self):
+        """The output tensor [tokens, d_model] (valid after plan())."""
+        if self._out_id is not None:
+            return self.graph.tensor(self._out_id)
+        return self._out
 
     def plan(self):
         arena, sym = self.graph.plan()

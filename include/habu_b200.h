@@ -196,6 +196,16 @@ size_t hb_p2p_flag_bytes(void);
 hb_status hb_p2p_attach_external(hb_ctx* ctx, int32_t world, int32_t rank,
                                  const void* const* peer_ptrs, void* multicast_ptr, size_t bytes);
 hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo);
+/* Fused collective for the tensor-parallel block: reduce-scatter of the row-parallel
+ * partial products, residual add and RMSNorm on this rank's rows/world rows, all-gather of
+ * the normalised rows -- one kernel over peer memory (HB_AR_P2P) or through NVSwitch
+ * (HB_AR_NVLS), bf16.  `partial` and `out` are [rows, cols] inside the symmetric buffer;
+ * `residual_in` / `residual_out` are local [rows, cols] of which only this rank's rows are
+ * read / written: residual_out = bf16(residual_in + bf16(sum of partials)).
+ * mode 0: out = rmsnorm(residual_out) * gain; mode 1: out = residual_out (final gather). */
+hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const void* gain,
+                             const void* residual_in, void* residual_out, void* out,
+                             int64_t rows, int64_t cols, float eps, int32_t mode, int32_t algo);
 
 /* ---- model-IR executor: node list, memory planner, launcher --------------------------
  * A graph is an ordered list of operator nodes over tensor ids.  `hb_graph_plan` computes
@@ -215,7 +225,9 @@ enum {
   HB_NODE_SWIGLU = 6,      /* in: x */
   HB_NODE_GELU = 7,        /* in: x */
   HB_NODE_ADD = 8,         /* in: a, b */
-  HB_NODE_ARGMAX = 9       /* in: x */
+  HB_NODE_ARGMAX = 9,      /* in: x */
+  HB_NODE_AR_NORM = 10     /* in: partial, [gain], residual_in, residual_out (written); out: normalised
+                              or gathered rows   iparam: mode, algorithm   fparam: eps */
 };
 enum { HB_T_SYMMETRIC = 1 };
 typedef struct hb_node {

@@ -68,11 +68,13 @@ def _tp_rank(rank, world):
     ref = decoder.forward(CFG, x0, layers, round_bf16=True)
     xb = oracle.to_bf16_bits(x0)
     outs = {}
-    cases = [("nccl", hb.HB_AR_NCCL, 1), ("p2p", hb.HB_AR_AUTO, 1), ("p2p-overlap", hb.HB_AR_AUTO, 2)]
+    cases = [("nccl", hb.HB_AR_NCCL, 1), ("p2p", hb.HB_AR_AUTO, 1), ("p2p-overlap", hb.HB_AR_AUTO, 2),
+             ("p2p-fused", hb.HB_AR_AUTO, 1)]
     graphs = {}
     need = 0
     for name, algo, chunks in cases:
-        dg = DecoderGraph(ctx, CFG, world, rank, [_bits(shard_layer(l, CFG, world, rank)) for l in layers], algo, chunks)
+        dg = DecoderGraph(ctx, CFG, world, rank, [_bits(shard_layer(l, CFG, world, rank)) for l in layers], algo, chunks,
+                          fused=name.endswith("fused"))
         _, sym = dg.plan()
         need = max(need, sym)
         graphs[name] = dg
@@ -100,6 +102,8 @@ def _tp_rank(rank, world):
         assert all(g == gathered[0] for g in gathered), "ranks disagree"
         dist.barrier()
     assert np.array_equal(outs["p2p"], outs["p2p-overlap"]), "chunked overlap changed the result"
+    # the fused reduce-scatter / norm / all-gather nodes round at the same points
+    assert np.array_equal(outs["p2p"], outs["p2p-fused"]), "fused collective changed the result"
     ctx.close()
     dist.destroy_process_group()
 
