@@ -231,10 +231,25 @@ hb_allreduce_nvls_kernel(const ArParams p, char* mc) {
   const int64_t per = (nvec + p.world - 1) / p.world;
   const int64_t v0 = per * p.rank;
   const int64_t v1 = min(nvec, v0 + per);
-  for (int64_t i = v0 + cta * (int64_t)AR_THREADS + threadIdx.x; i < v1; i += (int64_t)gridDim.x * AR_THREADS) {
-    char* a = mc + p.data_off + i * 16;
-    const uint4 v = sizeof(T) == 2 ? multimem_ld_reduce_bf16(a) : multimem_ld_reduce_f32(a);
-    multimem_st(a, v);
+  // Four reductions in flight per thread: a switch round trip is several microseconds, so
+  // the bytes in flight, not the SM count, set the rate.
+  constexpr int U = 4;
+  const int64_t step = (int64_t)gridDim.x * AR_THREADS;
+  for (int64_t i = v0 + cta * (int64_t)AR_THREADS + threadIdx.x; i < v1; i += step * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t j = i + u * step;
+      if (j < v1) {
+        char* a = mc + p.data_off + j * 16;
+        v[u] = sizeof(T) == 2 ? multimem_ld_reduce_bf16(a) : multimem_ld_reduce_f32(a);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t j = i + u * step;
+      if (j < v1) multimem_st(mc + p.data_off + j * 16, v[u]);
+    }
   }
   if (p.rank == 0 && cta == 0 && threadIdx.x < (int)(p.count % N)) {
     const int64_t e = nvec * N + threadIdx.x;
@@ -474,7 +489,7 @@ extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32
 // ---------------------------------------------------------------------------------------
 namespace {
 
-constexpr int ARN_MAX_VEC = 8;   // cols <= 256 * 8 * 8 = 16384
+constexpr int ARN_MAX_VEC = 4;   // cols <= 256 * 4 * 8 = 8192 (two rows of operands stay in registers)
 
 struct ArnParams {
   ArParams ar;                 // peers, flag block, world/rank, epoch (data_off = partial's offset)
@@ -496,17 +511,16 @@ hb_allreduce_norm_kernel(const ArnParams p) {
   if (!ar_barrier(p.ar, 0, cta)) return;
   const int per = p.rows / p.ar.world;
   const int row0 = per * p.ar.rank;
-  for (int row = row0 + cta; row < row0 + per; row += gridDim.x) {
+  // The partial sums of the NEXT row are requested before the current row is normalised,
+  // so two rows' worth of switch (or peer) reads are in flight per CTA.
+  auto fetch = [&](int row, uint4 (&dst)[ARN_MAX_VEC]) {
     const int64_t base = static_cast<int64_t>(row) * p.cols8;
-    float v[ARN_MAX_VEC][8];
-    float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < ARN_MAX_VEC; ++k) {
       const int c = threadIdx.x + k * AR_THREADS;
       if (c < p.cols8) {
-        uint4 s4;
         if (NVLS) {
-          s4 = multimem_ld_reduce_bf16(p.mc + p.ar.data_off + (base + c) * 16);
+          dst[k] = multimem_ld_reduce_bf16(p.mc + p.ar.data_off + (base + c) * 16);
         } else {
           uint4 pv[WORLD];
 #pragma unroll
@@ -517,8 +531,24 @@ hb_allreduce_norm_kernel(const ArnParams p) {
 #pragma unroll
           for (int r = 0; r < WORLD; ++r)
             if (r < p.ar.world) Vec<__nv_bfloat16>::add(acc, pv[r]);
-          s4 = Vec<__nv_bfloat16>::pack(acc);
+          dst[k] = Vec<__nv_bfloat16>::pack(acc);
         }
+      }
+    }
+  };
+  uint4 cur[ARN_MAX_VEC], nxt[ARN_MAX_VEC];
+  if (row0 + cta < row0 + per) fetch(row0 + cta, cur);
+  for (int row = row0 + cta; row < row0 + per; row += gridDim.x) {
+    const int64_t base = static_cast<int64_t>(row) * p.cols8;
+    const bool more = row + (int)gridDim.x < row0 + per;
+    if (more) fetch(row + gridDim.x, nxt);
+    float v[ARN_MAX_VEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < ARN_MAX_VEC; ++k) {
+      const int c = threadIdx.x + k * AR_THREADS;
+      if (c < p.cols8) {
+        const uint4 s4 = cur[k];
         const uint4 r4 = p.residual_in[base + c];
         const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w}, rw[4] = {r4.x, r4.y, r4.z, r4.w};
         uint32_t xw[4];
@@ -578,6 +608,10 @@ hb_allreduce_norm_kernel(const ArnParams p) {
             if (r < p.ar.world) *(reinterpret_cast<uint4*>(static_cast<char*>(p.ar.peers[r]) + p.out_off) + base + c) = o4;
         }
       }
+    }
+    if (more) {
+#pragma unroll
+      for (int k = 0; k < ARN_MAX_VEC; ++k) cur[k] = nxt[k];
     }
   }
   ar_barrier(p.ar, 1, cta);

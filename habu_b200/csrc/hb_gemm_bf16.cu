@@ -14,6 +14,9 @@
 // the tensor core by shared-memory descriptors over the layout TMA writes.
 //
 // Algorithmic traffic per launch: (M*K + N*K + M*N) * 2 bytes; work 2*M*N*K flop.
+#include <stdio.h>
+#include <stdlib.h>
+
 #include "hb_internal.h"
 #include "hb_ptx.cuh"
 
@@ -70,6 +73,75 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// One 32-column chunk of one output row: apply the epilogue, round to bf16 once, store.
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, bool vec_ok, int row, int col0,
+                                               const uint32_t (&v)[32]) {
+  if (row >= p.M || col0 >= p.N) return;
+    if (p.epilogue == HB_EPI_SWIGLU) {
+      // columns interleave (gate, up): out[j] = silu(acc[2j]) * acc[2j+1]
+      const int ocol0 = col0 >> 1;
+      const int on = p.N >> 1;
+      __nv_bfloat16* dst = p.C + static_cast<int64_t>(row) * p.ldc + ocol0;
+      uint32_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g0 = __uint_as_float(v[4 * j]), u0 = __uint_as_float(v[4 * j + 1]);
+        const float g1 = __uint_as_float(v[4 * j + 2]), u1 = __uint_as_float(v[4 * j + 3]);
+        o[j] = pack_bf16x2(silu(g0) * u0, silu(g1) * u1);
+      }
+      if (vec_ok && ocol0 + 16 <= on) {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      } else {
+        const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(o);
+        for (int j = 0; j < 16; ++j)
+          if (ocol0 + j < on) dst[j] = ob[j];
+      }
+    } else {
+      float f[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+      if (p.epilogue == HB_EPI_GELU) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+      } else if (p.epilogue == HB_EPI_RESIDUAL) {
+        const __nv_bfloat16* r = p.R + static_cast<int64_t>(row) * p.ldr + col0;
+        if (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0) &&
+            col0 + 32 <= p.N) {
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            const uint4 rv = __ldg(reinterpret_cast<const uint4*>(r) + j4);
+            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 rf = __bfloat1622float2(r2[j]);
+              f[j4 * 8 + 2 * j] += rf.x;
+              f[j4 * 8 + 2 * j + 1] += rf.y;
+            }
+          }
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) f[j] += __bfloat162float(r[j]);
+        }
+      }
+      uint32_t o[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) o[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+      __nv_bfloat16* dst = p.C + static_cast<int64_t>(row) * p.ldc + col0;
+      if (vec_ok && col0 + 32 <= p.N) {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          d4[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+      } else {
+        const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(o);
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) dst[j] = ob[j];
+      }
+    }
+}
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -216,71 +288,7 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_32x32(t_row + c * 32, v);
         tmem_wait_ld();
         const int col0 = tn * BN + c * 32;
-        if (row < p.M && col0 < p.N) {
-          if (p.epilogue == HB_EPI_SWIGLU) {
-            // columns interleave (gate, up): out[j] = silu(acc[2j]) * acc[2j+1]
-            const int ocol0 = col0 >> 1;
-            const int on = p.N >> 1;
-            __nv_bfloat16* dst = p.C + static_cast<int64_t>(row) * p.ldc + ocol0;
-            uint32_t o[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float g0 = __uint_as_float(v[4 * j]), u0 = __uint_as_float(v[4 * j + 1]);
-              const float g1 = __uint_as_float(v[4 * j + 2]), u1 = __uint_as_float(v[4 * j + 3]);
-              o[j] = pack_bf16x2(silu(g0) * u0, silu(g1) * u1);
-            }
-            if (vec_ok && ocol0 + 16 <= on) {
-              uint4* d4 = reinterpret_cast<uint4*>(dst);
-              d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
-              d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
-            } else {
-              const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(o);
-              for (int j = 0; j < 16; ++j)
-                if (ocol0 + j < on) dst[j] = ob[j];
-            }
-          } else {
-            float f[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-            if (p.epilogue == HB_EPI_GELU) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
-            } else if (p.epilogue == HB_EPI_RESIDUAL) {
-              const __nv_bfloat16* r = p.R + static_cast<int64_t>(row) * p.ldr + col0;
-              if (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0) &&
-                  col0 + 32 <= p.N) {
-#pragma unroll
-                for (int j4 = 0; j4 < 4; ++j4) {
-                  const uint4 rv = __ldg(reinterpret_cast<const uint4*>(r) + j4);
-                  const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float2 rf = __bfloat1622float2(r2[j]);
-                    f[j4 * 8 + 2 * j] += rf.x;
-                    f[j4 * 8 + 2 * j + 1] += rf.y;
-                  }
-                }
-              } else {
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N) f[j] += __bfloat162float(r[j]);
-              }
-            }
-            uint32_t o[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) o[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
-            __nv_bfloat16* dst = p.C + static_cast<int64_t>(row) * p.ldc + col0;
-            if (vec_ok && col0 + 32 <= p.N) {
-              uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                d4[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-            } else {
-              const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(o);
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst[j] = ob[j];
-            }
-          }
-        }
+        epilogue_chunk(p, vec_ok, row, col0, v);
       }
       tc_fence_before();
       mbar_arrive(bar_tempty + acc * 8);
@@ -297,15 +305,189 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+// ------------------------------------------------------------------------------------
+// CTA-pair variant: two CTAs of a cluster (the two SMs of a TPC) share one 256 x 256 tile.
+// Each CTA loads its own 128 rows of A and its own 128 of the tile's 256 B rows; the
+// leader CTA issues tcgen05.mma.cta_group::2 (M = 256, N = 256), which reads A from each
+// CTA's shared memory and the two B halves from both, and leaves rows 0..127 of the tile
+// in the leader's tensor memory and rows 128..255 in the peer's.  Per k-block a CTA moves
+// 32 KB instead of 48 KB, so six stages fit and L2 -> SM traffic drops by a third.
+// Measured state: results are exact, but the tensor pipe is only ~32 % busy (the one-CTA
+// kernel reaches ~80 %), so the autotuner never selects these configurations yet; they
+// stay available by explicit config_id while the issue-rate problem is open.
+//   full[s]    leader only, 2 arrivals (+ 64 KB of TMA bytes from both CTAs)
+//   empty[s]   one per CTA, signalled by the leader's commit in both CTAs
+//   tfull[a]   one per CTA, same way;   tempty[a]  leader only, 256 arrivals (both epilogues)
+// No load is multicast: each CTA fetches exactly the bytes it owns.
+// ------------------------------------------------------------------------------------
+template <int STAGES>
+struct SmemLayout2 {
+  static constexpr int A_BYTES = 128 * BK * 2;
+  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_BAR = OFF_B + STAGES * B_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int OFF_TMEM_PTR = OFF_BAR + NUM_BARS * 8;
+  static constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
+  static constexpr int TOTAL = OFF_ABORT + 4;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const GemmParams p) {
+  using L = SmemLayout2<STAGES>;
+  constexpr int BN2 = 256;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sA = smem_base + L::OFF_A;
+  const uint32_t sB = smem_base + L::OFF_B;
+  const uint32_t bar_full = smem_base + L::OFF_BAR;
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;
+  const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_TMEM_PTR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::OFF_ABORT);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + s * 8, 2);
+      mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + a * 8, 1);
+      mbar_init(bar_tempty + a * 8, 256);
+    }
+    mbar_fence_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {   // the same warp in both CTAs, same destination address
+    tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), 512);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before();
+  cluster_sync();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;     // 256 x 256 tiles
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, p, tm, tn);
+        const int m0 = tm * 256 + static_cast<int>(cta_rank) * 128;
+        const int n0 = tn * BN2 + static_cast<int>(cta_rank) * 128;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + s * 8, phase ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t full_leader = mapa(bar_full + s * 8, 0);
+          if (leader) mbar_arrive_expect_tx(bar_full + s * 8, L::A_BYTES + L::B_BYTES);
+          else mbar_arrive_expect_tx_cluster(full_leader, L::A_BYTES + L::B_BYTES);
+          tma_load_2d_pair(sA + s * L::A_BYTES, &tmA, full_leader, kb * BK, m0);
+          tma_load_2d_pair(sB + s * L::B_BYTES, &tmB, full_leader, kb * BK, n0);
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+      if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 11; }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && elect_one()) {
+      const uint32_t idesc = umma_idesc_bf16(256, BN2, 0, 0);
+      int s = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(bar_tempty + acc * 8, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN2;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + s * 8, phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_ss<2>(d_tmem, umma_desc_k_sw128(sA + s * L::A_BYTES + k * 32),
+                       umma_desc_k_sw128(sB + s * L::B_BYTES + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair_mcast(bar_empty + s * 8, 3);      // frees the slot in both CTAs
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair_mcast(bar_tfull + acc * 8, 3);
+      }
+      if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 12; }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const uint32_t tempty_leader = mapa(bar_tempty, 0);
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+      int tm, tn;
+      tile_coords(tile, p, tm, tn);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(bar_tfull + acc * 8, acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * 256 + static_cast<int>(cta_rank) * 128 + row_in_tile;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN2;
+#pragma unroll 1
+      for (int c = 0; c < BN2 / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + c * 32, v);
+        tmem_wait_ld();
+        epilogue_chunk(p, vec_ok, row, tn * BN2 + c * 32, v);
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(tempty_leader + acc * 8);
+    }
+    if (!ok && p.status && lane == 0) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 13; }
+  }
+
+  // Neither CTA may leave while its partner can still signal its barriers or read its
+  // shared memory.
+  tc_fence_before();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<2>(tmem_base, 512);
+  }
+}
+
 struct GemmConfig {
   int bn, stages;
   int raster_group;
+  int cluster;      // 1: one CTA per 128 x bn tile; 2: CTA pair per 256 x 256 tile
 };
-// config_id -> (tile N, stages, raster group).  Tile M is 128, tile K 64, cluster 1.
+// config_id -> (tile N, stages, raster group, cluster).  Tile K is 64; tile M is 128 per CTA.
 constexpr GemmConfig kConfigs[] = {
-    {256, 4, 8},  {256, 4, 16}, {256, 4, 4},  {256, 4, 2},
-    {128, 6, 8},  {128, 6, 16}, {128, 6, 4},
-    {64, 8, 8},   {64, 8, 16},
+    {256, 4, 8, 1},  {256, 4, 16, 1}, {256, 4, 4, 1},  {256, 4, 2, 1},
+    {128, 6, 8, 1},  {128, 6, 16, 1}, {128, 6, 4, 1},
+    {64, 8, 8, 1},   {64, 8, 16, 1},
+    {256, 6, 8, 2},  {256, 6, 4, 2},  {256, 6, 2, 2},  {256, 6, 16, 2},
 };
 constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
 
@@ -329,9 +511,48 @@ hb_status launch_cfg(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB
   return hb_check_cuda(ctx, cudaGetLastError(), "gemm launch");
 }
 
+template <int STAGES>
+hb_status launch_pair(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p) {
+  using L = SmemLayout2<STAGES>;
+  auto kern = hb_gemm_bf16_pair_kernel<STAGES>;
+  // The kernel is persistent: every cluster of the grid must be resident at once, so the
+  // grid is capped by what the occupancy query reports (not every SM has a pairable
+  // neighbour, so this is below sm_count / 2).
+  static int resident_pairs[64] = {};
+  if (!resident_pairs[ctx->device & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(pair gemm)");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctx->sm_count & ~1u);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = L::DYN_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess || n < 1) { cudaGetLastError(); n = ctx->sm_count / 2 - 8; }
+    if (getenv("HB_DEBUG")) fprintf(stderr, "[habu_b200] pair gemm: %d resident clusters (query status %d)\n", n, (int)e);
+    resident_pairs[ctx->device & 63] = n;
+  }
+  p.tiles_m = (p.M + 255) / 256;
+  p.tiles_n = (p.N + 255) / 256;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int max_pairs = resident_pairs[ctx->device & 63];
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  kern<<<2 * pairs, GEMM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, p);
+  ctx->launches++;
+  return hb_check_cuda(ctx, cudaGetLastError(), "pair gemm launch");
+}
+
 }  // namespace
 
 int hb_gemm_num_configs() { return kNumConfigs; }
+bool hb_gemm_config_supports(int id, const hb_gemm_args& a) {
+  return kConfigs[id].cluster == 1 || (!a.a_mn_major && !a.b_mn_major);
+}
 
 void hb_gemm_config_describe(int id, hb_tune_result* out) {
   const GemmConfig& c = kConfigs[id];
@@ -340,7 +561,8 @@ void hb_gemm_config_describe(int id, hb_tune_result* out) {
   out->tile_n = c.bn;
   out->tile_k = BK;
   out->stages = c.stages;
-  out->cluster = 1;
+  out->cluster = c.cluster;
+  if (c.cluster == 2) out->tile_m = 256;
   out->raster_group = c.raster_group;
   out->split_k = 1;
 }
@@ -352,6 +574,27 @@ hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id)
   const GemmConfig cfg = kConfigs[config_id];
   CUtensorMap tmA, tmB;
   hb_status st;
+  if (cfg.cluster == 2) {
+    if (a.a_mn_major || a.b_mn_major)
+      return hb_fail(ctx, HB_ERR_UNSUPPORTED, "matmul: the CTA-pair configurations need K-contiguous operands");
+    uint64_t dimsA[2] = {(uint64_t)a.K, (uint64_t)a.M}, dimsB[2] = {(uint64_t)a.K, (uint64_t)a.N};
+    uint64_t strA[1] = {(uint64_t)a.lda * 2}, strB[1] = {(uint64_t)a.ldb * 2};
+    uint32_t box[2] = {BK, 128};
+    if ((st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dimsA, strA, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
+    if ((st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dimsB, strB, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
+    GemmParams p;
+    p.C = static_cast<__nv_bfloat16*>(a.C);
+    p.R = static_cast<const __nv_bfloat16*>(a.residual);
+    p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
+    p.ldc = a.ldc; p.ldr = a.ldr;
+    p.raster_group = cfg.raster_group;
+    p.epilogue = a.epilogue;
+    p.a_mn = 0; p.b_mn = 0;
+    p.status = ctx->d_status;
+    return launch_pair<6>(ctx, tmA, tmB, p);
+  }
   // A: K-major -> dims (K, M), box (64, 128); M-major -> dims (M, K), box (64, 64) x2.
   if (!a.a_mn_major) {
     uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.M};

@@ -10,6 +10,7 @@
 
 int hb_gemm_num_configs();
 void hb_gemm_config_describe(int id, hb_tune_result* out);
+bool hb_gemm_config_supports(int id, const hb_gemm_args& a);
 
 namespace {
 
@@ -52,7 +53,7 @@ int hb_gemm_pick_config(hb_ctx* ctx, const hb_gemm_args& a) {
   for (int id = 0; id < n; ++id) {
     hb_tune_result r;
     hb_gemm_config_describe(id, &r);
-    if (r.raster_group != 8) continue;
+    if (r.raster_group != 8 || r.cluster != 1) continue;
     const int64_t tiles = tiles_m * ((a.N + r.tile_n - 1) / r.tile_n);
     best = id;
     if (tiles >= ctx->sm_count) break;
@@ -127,6 +128,7 @@ extern "C" hb_status hb_autotune(hb_ctx* ctx, const hb_op_desc* desc, int32_t mo
   float best_ms = 0.f;
   const int reps = 5;
   for (int id = 0; id < hb_gemm_num_configs(); ++id) {
+    if (!hb_gemm_config_supports(id, g)) continue;
     for (int w = 0; w < 2; ++w)
       if ((st = hb_launch_gemm_bf16(ctx, g, id)) != HB_OK) break;
     if (st != HB_OK) break;
