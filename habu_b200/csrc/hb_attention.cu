@@ -52,8 +52,8 @@ struct Smem {
   static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;              // KV_STAGES tiles
   static constexpr int OFF_V = OFF_K + KV_STAGES * TILE_BYTES;
   static constexpr int OFF_BAR = OFF_V + KV_STAGES * TILE_BYTES;
-  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], o_full[2]
-  static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 6;
+  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2][2 halves], o_full[2]
+  static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 8;
   static constexpr int OFF_TMEM_PTR = OFF_BAR + NUM_BARS * 8;
   static constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
   static constexpr int TOTAL = OFF_ABORT + 4;
@@ -77,7 +77,7 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   const uint32_t bar_v_empty = bar_v_full + KV_STAGES * 8;
   const uint32_t bar_s_full = bar_v_empty + KV_STAGES * 8;
   const uint32_t bar_p_ready = bar_s_full + 2 * 8;
-  const uint32_t bar_o_full = bar_p_ready + 2 * 8;
+  const uint32_t bar_o_full = bar_p_ready + 4 * 8;
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + Smem::OFF_TMEM_PTR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::OFF_ABORT);
 
@@ -116,7 +116,8 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + t * 8, 1);
-      mbar_init(bar_p_ready + t * 8, 128);
+      mbar_init(bar_p_ready + (t * 2) * 8, 128);
+      mbar_init(bar_p_ready + (t * 2 + 1) * 8, 128);
       mbar_init(bar_o_full + t * 8, 1);
     }
     mbar_fence_init();
@@ -175,13 +176,13 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         umma_commit<1>(bar_s_full + t * 8);
       };
-      auto issue_pv = [&](int t, int j) {
+      auto issue_pv = [&](int t, int j, int hf) {     // keys [64 hf, 64 hf + 64) of the tile
         const int s = j % KV_STAGES;
         const uint32_t d_tmem = tmem_base + 256 + t * 128;
         const uint32_t a_tmem = tmem_base + t * 128;     // P aliases S: 64 packed columns
         const uint32_t b_addr = sV + s * TILE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk)
+        for (int kk = hf * 4; kk < hf * 4 + 4; ++kk)
           umma_ts(d_tmem, a_tmem + kk * 8, umma_desc_mn_sw128(b_addr + kk * 2048, HALF_BYTES, 1024), idesc_pv,
                   (j | kk) != 0 ? 1u : 0u);
       };
@@ -205,9 +206,12 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         if (!mbar_wait(bar_v_full + s * 8, ph, abort_flag)) { ok = false; break; }
         for (int t = 0; t < 2; ++t) {
           if (j < n_t[t]) {
-            if (!mbar_wait(bar_p_ready + t * 8, j & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(bar_p_ready + (t * 2) * 8, j & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            issue_pv(t, j);
+            issue_pv(t, j, 0);
+            if (!mbar_wait(bar_p_ready + (t * 2 + 1) * 8, j & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, j, 1);
             if (j + 1 == n_t[t]) umma_commit<1>(bar_o_full + t * 8);
           }
           if (j + 1 < n_t[t]) {
@@ -288,28 +292,29 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
       }
       const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref * p.scale_log2;
-      float l0 = 0.f, l1 = 0.f;
+      // P is produced and published in two halves of 64 keys: the PV product starts on the
+      // first half while the second is still being exponentiated.
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t pk[8];
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float e0 = ex2_approx(fmaf(__uint_as_float(sv[c * 16 + 2 * i]), p.scale_log2, neg_m));
-          const float e1 = ex2_approx(fmaf(__uint_as_float(sv[c * 16 + 2 * i + 1]), p.scale_log2, neg_m));
-          l0 += e0;
-          l1 += e1;
+        for (int i = 0; i < 32; i += 2) {
+          const int e = hf * 64 + 2 * i;
+          const float e0 = ex2_approx(fmaf(__uint_as_float(sv[e]), p.scale_log2, neg_m));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, neg_m));
+          const float e2 = ex2_approx(fmaf(__uint_as_float(sv[e + 2]), p.scale_log2, neg_m));
+          const float e3 = ex2_approx(fmaf(__uint_as_float(sv[e + 3]), p.scale_log2, neg_m));
+          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
           pk[i] = pack_bf16x2(e0, e1);
+          pk[i + 1] = pack_bf16x2(e2, e3);
         }
-        // 8 packed columns = 16 keys
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};" ::"r"(pk[0]),
-                     "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7]),
-                     "r"(tS + c * 8)
-                     : "memory");
+        tmem_st_32x32(tS + hf * 32, pk);     // 32 packed columns = 64 keys
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p_ready + (t * 2 + hf) * 8);
       }
-      l += l0 + l1;
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_p_ready + t * 8);
+      l += (l0 + l1) + (l2 + l3);
     }
     // ---- epilogue: O / l -> bf16 -> global
     if (ok && n_mine > 0) {
