@@ -5,13 +5,14 @@
 //     M-side operand and A (padded to a multiple of 16 rows by TMA zero fill) is its N-side
 //     operand, so tcgen05.mma runs at M=128, N=16..64 and no tensor-core work is wasted on
 //     padding M up to 128;
-//   * K is split into `split` slices so that tiles * split CTAs cover the machine (two
-//     CTAs fit per SM); each CTA pipelines its slice through a TMA ring;
-//   * every CTA writes its fp32 partial tile to scratch; the last CTA to finish a tile
-//     (atomic ticket) adds the partials in slice order -- a fixed order, so the result is
-//     bit-identical run to run -- rounds to bf16 once and writes C.
-// Scratch: split * N * Mpad floats of partials plus one ticket per tile (tickets are left
-// at zero by the CTA that consumes them).
+//   * stream-K: the (tile, k-block) units are cut into one contiguous, equal range per CTA
+//     and one persistent CTA runs per SM with an 8..11-stage TMA ring (~200 KB in flight),
+//     so every SM streams the same number of bytes and pays one prologue;
+//   * a range that covers only part of a tile writes its fp32 partial to scratch; the last
+//     range to finish a tile (atomic ticket) adds the partials in k order -- a fixed order,
+//     so the result is bit-identical run to run -- rounds to bf16 once and writes C.
+// Scratch: tiles * max_segments * 128 * Mpad floats of partials plus one ticket per tile
+// (tickets are left at zero by the CTA that consumes them).
 // Algorithmic traffic per launch: (N*K + M*K + M*N) * 2 bytes.
 #include <stdlib.h>
 #include <string.h>
@@ -25,70 +26,72 @@ using namespace hb;
 
 constexpr int BN_ROWS = 128;   // rows of B per tile (MMA M)
 constexpr int BK = 64;
-constexpr int STAGES = 4;     // 4 x 24 KB: two CTAs fit in one SM's shared memory
+constexpr int MAX_STAGES = 12;
 constexpr int SK_THREADS = 192;
 constexpr int MAX_MPAD = 64;
+constexpr int B_BYTES = BN_ROWS * BK * 2;   // 16 KB
 
 struct SkinnyParams {
   __nv_bfloat16* C;
-  float* partial;      // [split][N_tiles*128][mpad]
-  int* tickets;        // [N_tiles]
+  float* partial;      // [tile][segment][128][mpad]
+  int* tickets;        // [tile]
   int M, N, K;
   int64_t ldc;
   int mpad;            // M rounded up to 16
-  int split;
-  int kb_per_split;    // k-blocks per slice
+  int stages;          // ring depth (<= MAX_STAGES)
+  int a_bytes;         // bytes of one A stage (mpad * 128)
+  int kps;             // 64-wide k-blocks fetched per stage (contiguous bytes per row = 128 * kps)
+  int num_kb;          // k-groups (of kps k-blocks) per tile
+  int tiles;
+  int max_seg;         // partial slots per tile
+  int64_t units;       // tiles * num_kb
   int32_t* status;
 };
 
-struct SkSmem {
-  static constexpr int B_BYTES = BN_ROWS * BK * 2;       // 16 KB
-  static constexpr int A_BYTES = MAX_MPAD * BK * 2;      // 8 KB (mpad rows used)
-  static constexpr int OFF_B = 0;
-  static constexpr int OFF_A = OFF_B + STAGES * B_BYTES;
-  static constexpr int OFF_BAR = OFF_A + STAGES * A_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 1;
-  static constexpr int OFF_TMEM_PTR = OFF_BAR + NUM_BARS * 8;
-  static constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
-  static constexpr int OFF_LAST = OFF_ABORT + 4;
-  static constexpr int TOTAL = OFF_LAST + 4;
-  static constexpr int DYN_BYTES = TOTAL + 1024;
-};
+// CTA that owns unit u when `units` are cut into `g` contiguous ranges [c*units/g, (c+1)*units/g).
+__device__ __forceinline__ int cta_of(int64_t u, int64_t units, int g) {
+  return static_cast<int>(((u + 1) * g - 1) / units);
+}
 
-__global__ void __launch_bounds__(SK_THREADS, 2)
+__global__ void __launch_bounds__(SK_THREADS, 1)
 hb_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmA,
                       const SkinnyParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t sB = smem_base + SkSmem::OFF_B;
-  const uint32_t sA = smem_base + SkSmem::OFF_A;
-  const uint32_t bar_full = smem_base + SkSmem::OFF_BAR;
-  const uint32_t bar_empty = bar_full + STAGES * 8;
-  const uint32_t bar_done = bar_empty + STAGES * 8;
-  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + SkSmem::OFF_TMEM_PTR);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + SkSmem::OFF_ABORT);
-  volatile int* is_last = reinterpret_cast<volatile int*>(smem + SkSmem::OFF_LAST);
+  // layout: B stages | A stages (1 KB aligned each) | barriers | tmem ptr | abort | last flag
+  const uint32_t a_box = (static_cast<uint32_t>(p.a_bytes) + 1023u) & ~1023u;
+  const uint32_t a_stride = a_box * p.kps;
+  const uint32_t b_stride = B_BYTES * p.kps;
+  const uint32_t sB = smem_base;
+  const uint32_t sA = sB + p.stages * b_stride;
+  const uint32_t bar_full = sA + p.stages * a_stride;
+  const uint32_t bar_empty = bar_full + MAX_STAGES * 8;
+  const uint32_t bar_tfull = bar_empty + MAX_STAGES * 8;
+  const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  uint8_t* tail = smem + (bar_tempty + 2 * 8 - smem_base);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
+  volatile int* is_last = reinterpret_cast<volatile int*>(tail + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tile = blockIdx.x / p.split;
-  const int slice = blockIdx.x % p.split;
-  const int n0 = tile * BN_ROWS;
-  const int num_kb_total = (p.K + BK - 1) / BK;
-  const int kb0 = slice * p.kb_per_split;
-  const int kb1 = min(num_kb_total, kb0 + p.kb_per_split);
-  const int num_kb = max(0, kb1 - kb0);
-  constexpr uint32_t TMEM_COLS = 64;
+  const int g = gridDim.x;
+  const int64_t u_begin = p.units * blockIdx.x / g;
+  const int64_t u_end = p.units * (blockIdx.x + 1) / g;
+  constexpr uint32_t TMEM_COLS = 128;        // two accumulators of up to 64 columns
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     *is_last = 0;
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < p.stages; ++s) {
       mbar_init(bar_full + s * 8, 1);
       mbar_init(bar_empty + s * 8, 1);
     }
-    mbar_init(bar_done, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + a * 8, 1);
+      mbar_init(bar_tempty + a * 8, 128);
+    }
     mbar_fence_init();
     fence_proxy_async_smem();
     tma_prefetch_desc(&tmA);
@@ -102,39 +105,56 @@ hb_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  const uint32_t a_bytes = static_cast<uint32_t>(p.mpad) * BK * 2;
 
   if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int64_t u = u_begin; u < u_end; ++u) {
+        const int tile = static_cast<int>(u / p.num_kb);
+        const int kb = static_cast<int>(u % p.num_kb);
         if (!mbar_wait(bar_empty + s * 8, phase ^ 1, abort_flag)) { ok = false; break; }
-        mbar_arrive_expect_tx(bar_full + s * 8, SkSmem::B_BYTES + a_bytes);
-        tma_load_2d(sB + s * SkSmem::B_BYTES, &tmB, bar_full + s * 8, kb * BK, n0);
-        tma_load_2d(sA + s * SkSmem::A_BYTES, &tmA, bar_full + s * 8, kb * BK, 0);
-        if (++s == STAGES) { s = 0; phase ^= 1; }
+        mbar_arrive_expect_tx(bar_full + s * 8, (B_BYTES + p.a_bytes) * p.kps);
+        for (int x = 0; x < p.kps; ++x) {   // consecutive k-blocks: 128 * kps contiguous bytes per row
+          tma_load_2d(sB + s * b_stride + x * B_BYTES, &tmB, bar_full + s * 8, (kb * p.kps + x) * BK, tile * BN_ROWS);
+          tma_load_2d(sA + s * a_stride + x * a_box, &tmA, bar_full + s * 8, (kb * p.kps + x) * BK, 0);
+        }
+        if (++s == p.stages) { s = 0; phase ^= 1; }
       }
       if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_SPLITK; p.status[2] = 1; }
     }
   } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
     if (elect_one()) {
       const uint32_t idesc = umma_idesc_bf16(BN_ROWS, p.mpad, 0, 0);
       int s = 0;
       uint32_t phase = 0;
+      int seg = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(bar_full + s * 8, phase, abort_flag)) { ok = false; break; }
+      for (int64_t u = u_begin; u < u_end && ok; ++seg) {
+        const int kb0 = static_cast<int>(u % p.num_kb);
+        const int64_t left = u_end - u;
+        const int nkb = static_cast<int>(left < p.num_kb - kb0 ? left : p.num_kb - kb0);
+        const int acc = seg & 1;
+        if (!mbar_wait(bar_tempty + acc * 8, ((seg >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        for (int i = 0; i < nkb; ++i) {
+          if (!mbar_wait(bar_full + s * 8, phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          for (int x = 0; x < p.kps; ++x) {
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k)
-          umma_ss<1>(tmem_base, umma_desc_k_sw128(sB + s * SkSmem::B_BYTES + k * 32),
-                     umma_desc_k_sw128(sA + s * SkSmem::A_BYTES + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
-        umma_commit<1>(bar_empty + s * 8);
-        if (++s == STAGES) { s = 0; phase ^= 1; }
+            for (int k = 0; k < BK / 16; ++k)
+              umma_ss<1>(tmem_base + acc * 64, umma_desc_k_sw128(sB + s * b_stride + x * B_BYTES + k * 32),
+                         umma_desc_k_sw128(sA + s * a_stride + x * a_box + k * 32), idesc, (i | x | k) != 0 ? 1u : 0u);
+          }
+          umma_commit<1>(bar_empty + s * 8);
+          if (++s == p.stages) { s = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit<1>(bar_tfull + acc * 8);
+        u += nkb;
       }
-      if (ok) umma_commit<1>(bar_done);
       if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_SPLITK; p.status[2] = 2; }
     }
   } else {
@@ -143,61 +163,82 @@ hb_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_cons
     const int r = q * 32 + lane;                 // row of the B slab = output column n0 + r
     const int etid = (warp - 2) * 32 + lane;     // 0..127
     bool ok = true;
-    if (num_kb > 0) ok = mbar_wait(bar_done, 0, abort_flag);
-    float acc[MAX_MPAD];
+    int seg = 0;
+    for (int64_t u = u_begin; u < u_end; ++seg) {
+      const int tile = static_cast<int>(u / p.num_kb);
+      const int kb0 = static_cast<int>(u % p.num_kb);
+      const int64_t left = u_end - u;
+      const int nkb = static_cast<int>(left < p.num_kb - kb0 ? left : p.num_kb - kb0);
+      u += nkb;
+      const int acc_i = seg & 1;
+      if (ok) ok = mbar_wait(bar_tfull + acc_i * 8, (seg >> 1) & 1, abort_flag);
+      float acc[MAX_MPAD];
 #pragma unroll
-    for (int i = 0; i < MAX_MPAD; ++i) acc[i] = 0.f;
-    if (ok && num_kb > 0) {
-      tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+      for (int i = 0; i < MAX_MPAD; ++i) acc[i] = 0.f;
+      if (ok) {
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc_i * 64;
 #pragma unroll
-      for (int c = 0; c < MAX_MPAD / 16; ++c) {
-        if (c * 16 < p.mpad) {
-          uint32_t v[16];
-          tmem_ld_32x16(t_row + c * 16, v);
-          tmem_wait_ld();
+        for (int c = 0; c < MAX_MPAD / 16; ++c) {
+          if (c * 16 < p.mpad) {
+            uint32_t v[16];
+            tmem_ld_32x16(t_row + c * 16, v);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[c * 16 + i] = __uint_as_float(v[i]);
+            for (int i = 0; i < 16; ++i) acc[c * 16 + i] = __uint_as_float(v[i]);
+          }
         }
+        tc_fence_before();
+        mbar_arrive(bar_tempty + acc_i * 8);    // the accumulator is in registers: free it
       }
-    }
-    const int64_t n_rows_padded = static_cast<int64_t>(gridDim.x / p.split) * BN_ROWS;
-    float* mine = p.partial + (static_cast<int64_t>(slice) * n_rows_padded + n0 + r) * p.mpad;
-    if (p.split > 1) {
+      const bool whole = nkb == p.num_kb;
+      bool write_out = whole;
+      if (!whole) {
+        // position of this range among the ranges that share the tile, in k order
+        const int64_t t0 = static_cast<int64_t>(tile) * p.num_kb;
+        const int c_first = cta_of(t0, p.units, g);
+        const int c_last = cta_of(t0 + p.num_kb - 1, p.units, g);
+        const int nseg = c_last - c_first + 1;
+        const int slot = static_cast<int>(blockIdx.x) - c_first;
+        float* base = p.partial + (static_cast<int64_t>(tile) * p.max_seg) * BN_ROWS * p.mpad;
+        float* mine = base + (static_cast<int64_t>(slot) * BN_ROWS + r) * p.mpad;
 #pragma unroll
-      for (int c = 0; c < MAX_MPAD / 4; ++c)
-        if (c * 4 < p.mpad)
-          *reinterpret_cast<float4*>(mine + c * 4) = make_float4(acc[c * 4], acc[c * 4 + 1], acc[c * 4 + 2], acc[c * 4 + 3]);
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (etid == 0) {
-        const int ticket = atomicAdd(p.tickets + tile, 1);
-        const int last = ticket == p.split - 1;
-        if (last) p.tickets[tile] = 0;           // leave the ticket ready for the next launch
-        *is_last = last;
-      }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (*is_last) {
+        for (int c = 0; c < MAX_MPAD / 4; ++c)
+          if (c * 4 < p.mpad)
+            *reinterpret_cast<float4*>(mine + c * 4) = make_float4(acc[c * 4], acc[c * 4 + 1], acc[c * 4 + 2], acc[c * 4 + 3]);
         __threadfence();
-#pragma unroll
-        for (int i = 0; i < MAX_MPAD; ++i) acc[i] = 0.f;
-        for (int s = 0; s < p.split; ++s) {      // fixed order: bit-identical run to run
-          const float* src = p.partial + (static_cast<int64_t>(s) * n_rows_padded + n0 + r) * p.mpad;
-#pragma unroll
-          for (int c = 0; c < MAX_MPAD / 4; ++c)
-            if (c * 4 < p.mpad) {
-              const float4 v = __ldcg(reinterpret_cast<const float4*>(src + c * 4));
-              acc[c * 4] += v.x; acc[c * 4 + 1] += v.y; acc[c * 4 + 2] += v.z; acc[c * 4 + 3] += v.w;
-            }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (etid == 0) {
+          const int ticket = atomicAdd(p.tickets + tile, 1);
+          const int last = ticket == nseg - 1;
+          if (last) p.tickets[tile] = 0;         // leave the ticket ready for the next launch
+          *is_last = last;
         }
-      }
-    }
-    if ((p.split == 1 || *is_last) && ok) {
-      const int n = n0 + r;
-      if (n < p.N) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        write_out = *is_last != 0;
+        if (write_out) {
+          __threadfence();
 #pragma unroll
-        for (int m = 0; m < MAX_MPAD; ++m)
-          if (m < p.M) p.C[static_cast<int64_t>(m) * p.ldc + n] = __float2bfloat16_rn(acc[m]);
+          for (int i = 0; i < MAX_MPAD; ++i) acc[i] = 0.f;
+          for (int sidx = 0; sidx < nseg; ++sidx) {   // k order: bit-identical run to run
+            const float* src = base + (static_cast<int64_t>(sidx) * BN_ROWS + r) * p.mpad;
+#pragma unroll
+            for (int c = 0; c < MAX_MPAD / 4; ++c)
+              if (c * 4 < p.mpad) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(src + c * 4));
+                acc[c * 4] += v.x; acc[c * 4 + 1] += v.y; acc[c * 4 + 2] += v.z; acc[c * 4 + 3] += v.w;
+              }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // is_last is rewritten by the next range
+      }
+      if (write_out && ok) {
+        const int n = tile * BN_ROWS + r;
+        if (n < p.N) {
+#pragma unroll
+          for (int m = 0; m < MAX_MPAD; ++m)
+            if (m < p.M) p.C[static_cast<int64_t>(m) * p.ldc + n] = __float2bfloat16_rn(acc[m]);
+        }
       }
     }
     if (!ok && p.status && lane == 0) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_SPLITK; p.status[2] = 3; }
@@ -211,34 +252,50 @@ hb_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_cons
   }
 }
 
+int skinny_kps() {
+  int k = 2;
+  if (const char* e = getenv("HB_SKINNY_KPS")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) k = v; }
+  return k;
+}
+int skinny_stages(int mpad, int kps) {
+  const int stage = kps * (B_BYTES + ((mpad * 128 + 1023) & ~1023));
+  int st = (200 * 1024) / stage;
+  return st > MAX_STAGES ? MAX_STAGES : st;
+}
+int skinny_smem_bytes(int mpad, int kps) {
+  const int stage = kps * (B_BYTES + ((mpad * 128 + 1023) & ~1023));
+  return skinny_stages(mpad, kps) * stage + (2 * MAX_STAGES + 4) * 8 + 16 + 1024;
+}
+
 }  // namespace
 
 bool hb_gemm_skinny_applicable(const hb_gemm_args& a) {
   return a.M <= MAX_MPAD && !a.a_mn_major && !a.b_mn_major && a.epilogue == HB_EPI_NONE && a.N >= 256;
 }
 
-// Chooses the K split and reports the scratch the launch needs.
-void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int* split, int* kb_per_split,
+// Chooses the grid and reports the scratch the launch needs: `grid` persistent CTAs, at
+// most `max_seg` ranges per tile, `partial_floats` floats of partials, `tiles` tickets.
+void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int* grid, int* max_seg,
                          size_t* partial_floats, int* tiles) {
   const int t = (int)((N + BN_ROWS - 1) / BN_ROWS);
-  const int num_kb = (int)((K + BK - 1) / BK);
+  const int kps = skinny_kps();
+  const int num_kb = (int)((K + BK * kps - 1) / (BK * kps));      // k-groups per tile
   const int mpad = (int)((M + 15) / 16) * 16;
-  int s = (2 * sm_count) / t;                  // one wave of two CTAs per SM
-  if (const char* e = getenv("HB_SKINNY_SPLIT")) s = atoi(e);
-  int max_s = num_kb / 8 > 0 ? num_kb / 8 : 1; // at least 8 k-blocks per slice
-  if (s > max_s) s = max_s;
-  if (s > 16) s = 16;
-  if (s < 1) s = 1;
-  int per = (num_kb + s - 1) / s;
-  s = (num_kb + per - 1) / per;                // drop empty slices
-  *split = s;
-  *kb_per_split = per;
+  const int64_t units = (int64_t)t * num_kb;
+  int g = sm_count;
+  if (const char* e = getenv("HB_SKINNY_CTAS")) { const int v = atoi(e); if (v >= 1) g = v; }
+  if (units / 4 < g) g = (int)(units / 4 > 0 ? units / 4 : 1);     // at least 4 k-groups per CTA
+  const int64_t per = units / g;                                     // shortest range
+  int ms = (int)((num_kb + per - 1) / per) + 1;
+  if (ms > g) ms = g;
+  *grid = g;
+  *max_seg = ms;
   *tiles = t;
-  *partial_floats = s > 1 ? (size_t)s * t * BN_ROWS * mpad : 0;
+  *partial_floats = (size_t)t * ms * BN_ROWS * mpad;
 }
 
 hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_gemm_args& a, float* partial, int* tickets,
-                                    int split, int kb_per_split, int tiles, int32_t* status) {
+                                    int grid, int max_seg, int tiles, int32_t* status) {
   CUtensorMap tmA, tmB;
   const int mpad = (int)((a.M + 15) / 16) * 16;
   {
@@ -265,8 +322,13 @@ hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_g
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.ldc = a.ldc;
   p.mpad = mpad;
-  p.split = split;
-  p.kb_per_split = kb_per_split;
+  p.kps = skinny_kps();
+  p.stages = skinny_stages(mpad, p.kps);
+  p.a_bytes = mpad * 128;
+  p.num_kb = (int)((a.K + BK * p.kps - 1) / (BK * p.kps));
+  p.tiles = tiles;
+  p.max_seg = max_seg;
+  p.units = (int64_t)tiles * p.num_kb;
   p.status = status;
   // the attribute is per device: one flag for each device this process launches on
   static bool attr_set_dev[64] = {};
@@ -274,27 +336,27 @@ hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_g
   if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
   bool& attr_set = attr_set_dev[dev & 63];
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(hb_gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SkSmem::DYN_BYTES);
+    int most = 0;
+    for (int m = 16; m <= MAX_MPAD; m += 16)
+      for (int k = 1; k <= 4; k *= 2) most = skinny_smem_bytes(m, k) > most ? skinny_smem_bytes(m, k) : most;
+    cudaError_t e = cudaFuncSetAttribute(hb_gemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(skinny gemm)");
     attr_set = true;
   }
-  hb_gemm_skinny_kernel<<<tiles * split, SK_THREADS, SkSmem::DYN_BYTES, stream>>>(tmB, tmA, p);
+  hb_gemm_skinny_kernel<<<grid, SK_THREADS, skinny_smem_bytes(mpad, p.kps), stream>>>(tmB, tmA, p);
   return hb_check_cuda(ctx, cudaGetLastError(), "skinny gemm launch");
 }
 
 hb_status hb_launch_gemm_skinny(hb_ctx* ctx, const hb_gemm_args& a) {
-  int split, per, tiles;
+  int grid, max_seg, tiles;
   size_t floats;
-  hb_gemm_skinny_plan(ctx->sm_count, a.M, a.N, a.K, &split, &per, &floats, &tiles);
+  hb_gemm_skinny_plan(ctx->sm_count, a.M, a.N, a.K, &grid, &max_seg, &floats, &tiles);
   if (tiles > HB_MAX_SPLITK_TILES) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "matmul: N too large for the split-K path");
   void* ws = nullptr;
-  if (floats) {
-    hb_status st = hb_get_scratch(ctx, HB_SCRATCH_WORKSPACE, floats * sizeof(float), &ws);
-    if (st != HB_OK) return st;
-  }
-  hb_status st = hb_launch_gemm_skinny_raw(ctx, ctx->stream, a, static_cast<float*>(ws), ctx->d_tickets, split, per, tiles,
-                                           ctx->d_status);
+  hb_status st = hb_get_scratch(ctx, HB_SCRATCH_WORKSPACE, floats * sizeof(float), &ws);
+  if (st != HB_OK) return st;
+  st = hb_launch_gemm_skinny_raw(ctx, ctx->stream, a, static_cast<float*>(ws), ctx->d_tickets, grid, max_seg, tiles,
+                                 ctx->d_status);
   if (st == HB_OK) ctx->launches++;
   return st;
 }
@@ -311,8 +373,9 @@ hb_status hb_launch_gemm_skinny(hb_ctx* ctx, const hb_gemm_args& a) {
 // context-owned buffer.  Every GPU that loads the library carries these arrays (about
 // 4 MiB) until the process exits.
 //
-// Limits: partials split * ceil(N/128)*128 * Mpad <= HB_STATIC_MAX_PARTIAL_FLOATS and
-// ceil(N/128) <= HB_STATIC_MAX_TILES; larger problems are refused with HB_ERR_UNSUPPORTED.
+// Limits: partials ceil(N/128) * segments * 128 * Mpad <= HB_STATIC_MAX_PARTIAL_FLOATS (segments
+// = ranges of K that can share one tile, 4 at N=K=8192 on 148 SMs) and ceil(N/128) <=
+// HB_STATIC_MAX_TILES; larger problems are refused with HB_ERR_UNSUPPORTED.
 // The first call on a device resolves the arrays' device addresses and sets the kernel's
 // shared-memory attribute; it should come before any stream capture.
 // All calls share the arrays: two calls that overlap on the GPU (different streams) race
@@ -389,9 +452,9 @@ extern "C" hb_status hb_matmul_skinny_static(const void* A, const void* B, void*
   StaticDev* d = nullptr;
   hb_status st = static_setup(device, &d);
   if (st != HB_OK) return st;
-  int split, per, tiles;
+  int grid, max_seg, tiles;
   size_t floats;
-  hb_gemm_skinny_plan(d->sm_count, M, N, K, &split, &per, &floats, &tiles);
+  hb_gemm_skinny_plan(d->sm_count, M, N, K, &grid, &max_seg, &floats, &tiles);
   if (tiles > HB_STATIC_MAX_TILES || floats > HB_STATIC_MAX_PARTIAL_FLOATS) {
     char detail[128];
     snprintf(detail, sizeof(detail), "needs %zu partial floats over %d tiles; the static scratch holds %zu floats and %d tiles",
@@ -406,7 +469,7 @@ extern "C" hb_status hb_matmul_skinny_static(const void* A, const void* B, void*
   a.A = A; a.B = B; a.C = C;
   a.M = M; a.N = N; a.K = K;
   a.lda = K; a.ldb = K; a.ldc = N;
-  st = hb_launch_gemm_skinny_raw(nullptr, stream, a, d->partial, d->tickets, split, per, tiles, d->status);
+  st = hb_launch_gemm_skinny_raw(nullptr, stream, a, d->partial, d->tickets, grid, max_seg, tiles, d->status);
   if (st != HB_OK) return static_fail(st, "skinny_static: launch failed (descriptor encoding or kernel launch)");
   return HB_OK;
 }

@@ -95,7 +95,7 @@ int hb_gemm_pick_config(hb_ctx* ctx, const hb_gemm_args& a);
 // Split-K path for M <= 64 (decode-shaped) products.
 bool hb_gemm_skinny_applicable(const hb_gemm_args& a);
 hb_status hb_launch_gemm_skinny(hb_ctx* ctx, const hb_gemm_args& a);
-void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int* split, int* kb_per_split,
+void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int* grid, int* max_seg,
                          size_t* partial_floats, int* tiles);
 hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_gemm_args& a, float* partial, int* tickets,
-                                    int split, int kb_per_split, int tiles, int32_t* status);
+                                    int grid, int max_seg, int tiles, int32_t* status);

@@ -109,8 +109,9 @@ hb_status hb_matmul_host(hb_ctx* ctx, const void* A_host, const void* B_host, vo
  * the process exits).  A [M,K] row-major, B column-major (N rows of K), C [M,N] row-major,
  * all bf16 device pointers; `device` must be the calling thread's current device and
  * `cuda_stream` a cudaStream_t (NULL = default stream).  Asynchronous.
- *   - Limit: split * ceil(N/128)*128 * roundup16(M) <= 2^20 partial floats and at most
- *     1024 column tiles; anything larger returns HB_ERR_UNSUPPORTED with a message.
+ *   - Limit: ceil(N/128) * segments * 128 * roundup16(M) <= 2^20 partial floats (segments:
+ *     the K ranges that can share one column tile, 4 at N=K=8192) and at most 1024 column
+ *     tiles; anything larger returns HB_ERR_UNSUPPORTED with a message.
  *   - The first call on a device looks up the static arrays' device addresses and sets
  *     the kernel's shared-memory attribute; make that first call before any stream capture.
  *   - All calls share the scratch: calls that overlap on the GPU race; serialise them.

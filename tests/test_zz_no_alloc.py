@@ -59,7 +59,7 @@ def test_static_scratch_refuses_problems_beyond_its_size(ctx):
     lib = model_ir._lib
     d = ctx.empty((8,))
     # refused before anything is launched, so the tiny buffer is never touched:
-    # 64 x 16384 x 65536 splits K in two and would need 2 * 16384 * 64 = 2^21 partial floats
+    # 64 x 16384 x 65536 needs 128 tiles x 3 K-ranges x 128 x 64 partial floats, over the 2^20 limit
     st = lib.hb_matmul_skinny_static(C.c_void_p(d.ptr), C.c_void_p(d.ptr), C.c_void_p(d.ptr), 64, 16384, 65536, 0, None)
     assert st == 7
     assert b"exceeds the static scratch" in lib.hb_static_last_error()
