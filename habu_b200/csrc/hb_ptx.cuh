@@ -45,13 +45,13 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 // Arrive on a barrier that lives in another CTA of the cluster (address from mapa).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(
                    bar_cluster_addr)
                : "memory");
 }
 // Same on a barrier in another CTA of the cluster (shared::cluster address from mapa).
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_cluster_addr, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(
                    bar_cluster_addr),
                "r"(bytes)
                : "memory");
