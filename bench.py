@@ -516,11 +516,15 @@ def main():
         else:
             value = wl.flop * world / (kern_ms * 1e-3) / 1e12
             achieved = wl.flop / (kern_ms * 1e-3) / 1e12
+        # Which measured peak applies: the burst figure for a short timed region, the sustained
+        # (power-capped) one for a region of a second or more.  Both fractions are reported.
         long_run = total_ms > 1000.0
         if wl.bound == "tensor":
             peak = pk["bf16_sustained"] if long_run else pk["bf16_burst"]
             roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "peak_kind": ("sustained" if long_run else "burst") + " cuBLAS bf16, of " + pk["source"]}
+                    "peak_kind": ("sustained" if long_run else "burst") + " cuBLAS bf16, of " + pk["source"],
+                    "frac_of_burst_peak": achieved / pk["bf16_burst"],
+                    "frac_of_sustained_peak": achieved / pk["bf16_sustained"]}
         else:
             achieved = wl.bytes / (kern_ms * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",

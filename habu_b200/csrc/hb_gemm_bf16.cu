@@ -402,8 +402,18 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint32_t full_leader = mapa(bar_full + s * 8, 0);
           if (leader) mbar_arrive_expect_tx(bar_full + s * 8, L::A_BYTES + L::B_BYTES);
           else mbar_arrive_expect_tx_cluster(full_leader, L::A_BYTES + L::B_BYTES);
-          tma_load_2d_pair(sA + s * L::A_BYTES, &tmA, full_leader, kb * BK, m0);
-          tma_load_2d_pair(sB + s * L::B_BYTES, &tmB, full_leader, kb * BK, n0);
+          if (!p.a_mn) {
+            tma_load_2d_pair(sA + s * L::A_BYTES, &tmA, full_leader, kb * BK, m0);
+          } else {   // M-major A: two boxes of 64 (M) x 64 (K)
+            tma_load_2d_pair(sA + s * L::A_BYTES, &tmA, full_leader, m0, kb * BK);
+            tma_load_2d_pair(sA + s * L::A_BYTES + L::A_BYTES / 2, &tmA, full_leader, m0 + 64, kb * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d_pair(sB + s * L::B_BYTES, &tmB, full_leader, kb * BK, n0);
+          } else {   // N-major B: two boxes of 64 (N) x 64 (K)
+            tma_load_2d_pair(sB + s * L::B_BYTES, &tmB, full_leader, n0, kb * BK);
+            tma_load_2d_pair(sB + s * L::B_BYTES + L::B_BYTES / 2, &tmB, full_leader, n0 + 64, kb * BK);
+          }
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
       }
@@ -412,7 +422,7 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (leader && elect_one()) {
-      const uint32_t idesc = umma_idesc_bf16(256, BN2, 0, 0);
+      const uint32_t idesc = umma_idesc_bf16(256, BN2, p.a_mn, p.b_mn);
       int s = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -427,9 +437,14 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           if (!mbar_wait(bar_full + s * 8, phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_ss<2>(d_tmem, umma_desc_k_sw128(sA + s * L::A_BYTES + k * 32),
-                       umma_desc_k_sw128(sB + s * L::B_BYTES + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t a_addr = sA + s * L::A_BYTES, b_addr = sB + s * L::B_BYTES;
+            const uint64_t ad = p.a_mn ? umma_desc_mn_sw128(a_addr + k * 2048, L::A_BYTES / 2, 1024)
+                                       : umma_desc_k_sw128(a_addr + k * 32);
+            const uint64_t bd = p.b_mn ? umma_desc_mn_sw128(b_addr + k * 2048, L::B_BYTES / 2, 1024)
+                                       : umma_desc_k_sw128(b_addr + k * 32);
+            umma_ss<2>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
           umma_commit_pair_mcast(bar_empty + s * 8, 3);      // frees the slot in both CTAs
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
@@ -551,7 +566,8 @@ hb_status launch_pair(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tm
 
 int hb_gemm_num_configs() { return kNumConfigs; }
 bool hb_gemm_config_supports(int id, const hb_gemm_args& a) {
-  return kConfigs[id].cluster == 1 || (!a.a_mn_major && !a.b_mn_major);
+  (void)a;
+  return id >= 0 && id < kNumConfigs;
 }
 
 void hb_gemm_config_describe(int id, hb_tune_result* out) {
@@ -575,14 +591,14 @@ hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id)
   CUtensorMap tmA, tmB;
   hb_status st;
   if (cfg.cluster == 2) {
-    if (a.a_mn_major || a.b_mn_major)
-      return hb_fail(ctx, HB_ERR_UNSUPPORTED, "matmul: the CTA-pair configurations need K-contiguous operands");
-    uint64_t dimsA[2] = {(uint64_t)a.K, (uint64_t)a.M}, dimsB[2] = {(uint64_t)a.K, (uint64_t)a.N};
+    // K-major operand: dims (K, rows), box (64, 128); MN-major: dims (rows, K), box (64, 64) twice
+    uint64_t dimsA[2] = {(uint64_t)(a.a_mn_major ? a.M : a.K), (uint64_t)(a.a_mn_major ? a.K : a.M)};
+    uint64_t dimsB[2] = {(uint64_t)(a.b_mn_major ? a.N : a.K), (uint64_t)(a.b_mn_major ? a.K : a.N)};
     uint64_t strA[1] = {(uint64_t)a.lda * 2}, strB[1] = {(uint64_t)a.ldb * 2};
-    uint32_t box[2] = {BK, 128};
-    if ((st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dimsA, strA, box,
+    uint32_t boxA[2] = {64, a.a_mn_major ? 64u : 128u}, boxB[2] = {64, a.b_mn_major ? 64u : 128u};
+    if ((st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dimsA, strA, boxA,
                                  CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
-    if ((st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dimsB, strB, box,
+    if ((st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dimsB, strB, boxB,
                                  CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
     GemmParams p;
     p.C = static_cast<__nv_bfloat16*>(a.C);
@@ -591,7 +607,7 @@ hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id)
     p.ldc = a.ldc; p.ldr = a.ldr;
     p.raster_group = cfg.raster_group;
     p.epilogue = a.epilogue;
-    p.a_mn = 0; p.b_mn = 0;
+    p.a_mn = a.a_mn_major; p.b_mn = a.b_mn_major;
     p.status = ctx->d_status;
     return launch_pair<6>(ctx, tmA, tmB, p);
   }

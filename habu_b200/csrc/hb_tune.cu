@@ -46,10 +46,9 @@ int hb_gemm_pick_config(hb_ctx* ctx, const hb_gemm_args& a) {
   auto it = ctx->tune_cache.find(hb_tune_key(d, ctx->sm_count, ctx->world));
   if (it != ctx->tune_cache.end() && it->second.config_id < hb_gemm_num_configs())
     return it->second.config_id;
-  // Heuristic: the CTA-pair 256 x 256 tile when both operands are K-contiguous and there is
-  // a tile for every pair of SMs; else the widest one-CTA tile that still gives every SM a tile.
+  // Heuristic: the CTA-pair 256 x 256 tile when there is a tile for every pair of SMs; else the widest one-CTA tile that still gives every SM a tile.
   const int n = hb_gemm_num_configs();
-  if (!a.a_mn_major && !a.b_mn_major && ((a.M + 255) / 256) * ((a.N + 255) / 256) >= ctx->sm_count / 2) {
+  if (((a.M + 255) / 256) * ((a.N + 255) / 256) >= ctx->sm_count / 2) {
     for (int id = 0; id < n; ++id) {
       hb_tune_result r;
       hb_gemm_config_describe(id, &r);

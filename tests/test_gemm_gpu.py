@@ -75,6 +75,10 @@ def test_bf16_mn_major_operands(ctx, a_mn, b_mn):
     assert max_abs(got, ref) < TOL_BF16
     got, ref = run_bf16(ctx, 200, 136, 72, a_mn=a_mn, b_mn=b_mn)
     assert max_abs(got, ref) < TOL_BF16
+    # every configuration (one-CTA tiles and CTA-pair tiles) on a ragged multi-tile shape
+    for i in range(len(hb.matmul_configs())):
+        got, ref = run_bf16(ctx, 520, 776, 200, a_mn=a_mn, b_mn=b_mn, config_id=i)
+        assert max_abs(got, ref) < TOL_BF16, i
 
 
 @pytest.mark.parametrize("epi", [hb.HB_EPI_GELU, hb.HB_EPI_SWIGLU, hb.HB_EPI_RESIDUAL])
