@@ -503,6 +503,7 @@ constexpr GemmConfig kConfigs[] = {
     {128, 6, 8, 1},  {128, 6, 16, 1}, {128, 6, 4, 1},
     {64, 8, 8, 1},   {64, 8, 16, 1},
     {256, 6, 8, 2},  {256, 6, 4, 2},  {256, 6, 2, 2},  {256, 6, 16, 2},
+    {256, 7, 8, 2},  {256, 7, 16, 2}, {256, 7, 4, 2},
 };
 constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
 
@@ -609,7 +610,7 @@ hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id)
     p.epilogue = a.epilogue;
     p.a_mn = a.a_mn_major; p.b_mn = a.b_mn_major;
     p.status = ctx->d_status;
-    return launch_pair<6>(ctx, tmA, tmB, p);
+    return cfg.stages == 7 ? launch_pair<7>(ctx, tmA, tmB, p) : launch_pair<6>(ctx, tmA, tmB, p);
   }
   // A: K-major -> dims (K, M), box (64, 128); M-major -> dims (M, K), box (64, 64) x2.
   if (!a.a_mn_major) {
