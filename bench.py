@@ -409,6 +409,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     import oracle
+    oracle.use_all_cores()
     wl = WORKLOADS[args.workload]()
     vals = []
     sample = ""
@@ -548,6 +549,7 @@ def main():
                           "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms}
             if world == 1 and rank == 0 and not args.no_cpu_baseline:
                 import oracle
+                oracle.use_all_cores()
                 v, sample = wl.cpu_sample()
                 res["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
                                        "sample": sample}

@@ -226,9 +226,6 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 1; }
-      // Drain: every armed load has landed once the consumer side has released (or the
-      // barrier phase completed); wait for the slots still in flight, bounded.
-      // (In the normal path the MMA warp consumed them already.)
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer

@@ -223,12 +223,8 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
       for (int j = 0; j < i && !written; ++j)
         written = root_of(g, g->nodes[j].out) == r ||
                   (g->nodes[j].kind == HB_NODE_AR_NORM && g->nodes[j].in[3] >= 0 && root_of(g, g->nodes[j].in[3]) == r);
-      const bool inout = (n.kind == HB_NODE_ROPE || n.kind == HB_NODE_ALL_REDUCE) && root_of(g, n.out) == r;
-      if (!written && !inout)
+      if (!written)
         return hb_fail(ctx, HB_ERR_INVALID, "graph: node %d (%s) reads planner-owned tensor %d before any node writes it", i,
-                       kNodeNames[n.kind], n.in[k]);
-      if (!written && inout)
-        return hb_fail(ctx, HB_ERR_INVALID, "graph: node %d (%s) updates tensor %d in place before any node writes it", i,
                        kNodeNames[n.kind], n.in[k]);
     }
   }

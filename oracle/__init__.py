@@ -46,6 +46,17 @@ def num_threads() -> int:
     return int(_lib.orc_num_threads())
 
 
+def use_all_cores() -> int:
+    """Let the checker use every core this process may run on (torchrun pins
+    OMP_NUM_THREADS=1 for its workers); returns the thread count now in use."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    _lib.orc_set_num_threads(C.c_int(n))
+    return num_threads()
+
+
 def round_bf16(x: np.ndarray) -> np.ndarray:
     """Round fp32 values to bf16 (nearest-even) in place; returns x."""
     _lib.orc_round_bf16(_f(x), _i64(x.size))

@@ -325,3 +325,6 @@ void orc_all_reduce(float** bufs, int world, int64_t n) {
   }
 }
 int orc_num_threads(void) { return omp_get_max_threads(); }
+/* torchrun exports OMP_NUM_THREADS=1 to its workers; the timed CPU baseline asks for the
+ * cores the process may actually use instead. */
+void orc_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }
