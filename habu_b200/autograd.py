@@ -119,8 +119,12 @@ class MlpTrainer:
             if i < self.n - 1:
                 h = tape.gelu(self.z[i], self.h[i])
         tape.mse(self.z[-1], y, self.dy, self.loss)
-        on_grad = (lambda g: ctx.all_reduce(g, self.algo)) if self.world > 1 else None
+        # each weight gradient is summed across ranks on the side stream while the main stream
+        # goes on with the remaining backward products
+        on_grad = (lambda g: ctx.all_reduce_async(g, self.algo)) if self.world > 1 else None
         tape.backward(self.scratch, on_grad)
+        if self.world > 1:
+            ctx.side_join()
         self.step_no += 1
         for i in range(self.n):
             ctx.adam_step(self.w32[i], self.m[i], self.v[i], self.grads[i], self.wb[i], self.step_no, self.lr, self.b1,

@@ -670,3 +670,47 @@ extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const 
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "all_reduce_norm launch");
 }
+
+// ---------------------------------------------------------------------------------------
+// Overlapped collectives outside the graph executor (the data-parallel trainer): the
+// allreduce is enqueued on the context's high-priority side stream, ordered after
+// everything already queued on the main stream; hb_side_join makes the main stream wait
+// for the side stream.  Between the two calls the main stream is free to run the kernels
+// that do not touch the reduced tensor (the rest of the backward pass).
+// ---------------------------------------------------------------------------------------
+static hb_status ensure_side_stream(hb_ctx* ctx) {
+  if (!ctx->side_stream) {
+    int lo = 0, hi = 0;
+    cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    cudaError_t e = cudaStreamCreateWithPriority(&ctx->side_stream, cudaStreamNonBlocking, hi);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaStreamCreate(side)");
+  }
+  if (!ctx->side_event) {
+    cudaError_t e = cudaEventCreateWithFlags(&ctx->side_event, cudaEventDisableTiming);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaEventCreate(side)");
+  }
+  return HB_OK;
+}
+
+extern "C" hb_status hb_all_reduce_async(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (ctx->world == 1) return HB_OK;
+  hb_status st = ensure_side_stream(ctx);
+  if (st != HB_OK) return st;
+  cudaStream_t main_stream = ctx->stream;
+  cudaError_t e = cudaEventRecord(ctx->side_event, main_stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->side_stream, ctx->side_event, 0);
+  if (e != cudaSuccess) return hb_check_cuda(ctx, e, "all_reduce_async: fork");
+  ctx->stream = ctx->side_stream;
+  st = hb_all_reduce(ctx, data, count, dtype, algo);
+  ctx->stream = main_stream;
+  return st;
+}
+
+extern "C" hb_status hb_side_join(hb_ctx* ctx) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!ctx->side_stream || !ctx->side_event) return HB_OK;
+  cudaError_t e = cudaEventRecord(ctx->side_event, ctx->side_stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, ctx->side_event, 0);
+  return hb_check_cuda(ctx, e, "side_join");
+}

@@ -43,6 +43,7 @@ struct hb_ctx {
   cudaStream_t stream = nullptr;      // stream in use
   cudaStream_t own_stream = nullptr;  // created by the context
   cudaStream_t side_stream = nullptr; // second stream for executor nodes that overlap (collectives)
+  cudaEvent_t side_event = nullptr;   // fork / join marker between the two streams
   int32_t* d_status = nullptr;
   int32_t* h_status = nullptr;        // pinned
   int* d_tickets = nullptr;           // split-K arrival tickets, one per output tile, zero between launches

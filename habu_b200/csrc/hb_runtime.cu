@@ -66,6 +66,7 @@ extern "C" hb_status hb_ctx_destroy(hb_ctx* ctx) {
   if (ctx->d_tickets) cudaFree(ctx->d_tickets);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  if (ctx->side_event) cudaEventDestroy(ctx->side_event);
   if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;

@@ -307,6 +307,17 @@ class Context:
         self._check(_lib.hb_all_reduce(self._h, x.ptr, n, x.dtype, algo))
         return x
 
+    def all_reduce_async(self, x: Tensor, algo: int = HB_AR_AUTO) -> Tensor:
+        """The allreduce on the side stream (after everything queued so far); pair with side_join()."""
+        n = 1
+        for s in x.shape:
+            n *= s
+        self._check(_lib.hb_all_reduce_async(self._h, x.ptr, n, x.dtype, algo))
+        return x
+
+    def side_join(self):
+        self._check(_lib.hb_side_join(self._h))
+
     # -- autotune entry point ---------------------------------------------------------
     def autotune(self, m: int, n: int, k: int, layout: int = 0, epilogue: int = HB_EPI_NONE,
                  search: bool = True) -> _capi.hb_tune_result:

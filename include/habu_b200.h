@@ -197,6 +197,12 @@ size_t hb_p2p_flag_bytes(void);
 hb_status hb_p2p_attach_external(hb_ctx* ctx, int32_t world, int32_t rank,
                                  const void* const* peer_ptrs, void* multicast_ptr, size_t bytes);
 hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo);
+/* Overlap: hb_all_reduce_async enqueues the same allreduce on the context's high-priority
+ * side stream, ordered after everything already queued on the main stream, and returns;
+ * hb_side_join makes the main stream wait for the side stream.  Kernels queued between the
+ * two calls must not touch the tensor being reduced. */
+hb_status hb_all_reduce_async(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo);
+hb_status hb_side_join(hb_ctx* ctx);
 /* Fused collective for the tensor-parallel block: reduce-scatter of the row-parallel
  * partial products, residual add and RMSNorm on this rank's rows/world rows, all-gather of
  * the normalised rows -- one kernel over peer memory (HB_AR_P2P) or through NVSwitch
