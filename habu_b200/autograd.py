@@ -87,8 +87,7 @@ class MlpTrainer:
         self.ctx, self.width, self.batch, self.n, self.world = ctx, width, batch, n_layers, world
         self.lr, self.b1, self.b2, self.eps, self.algo = lr, beta1, beta2, eps, algo
         self.step_no = 0
-        import oracle  # noqa: F401  (host-side bf16 conversion of the initial weights only)
-        from oracle import to_bf16_bits
+        from .model_ir import f32_to_bf16_bits as to_bf16_bits
         self.w32 = [ctx.upload(np.ascontiguousarray(w, np.float32)) for w in weights_f32]
         self.wb = [ctx.upload(to_bf16_bits(w)) for w in weights_f32]
         zeros = np.zeros((width, width), np.float32)

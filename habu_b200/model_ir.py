@@ -65,6 +65,14 @@ class Tensor:
         return t
 
 
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Host-side fp32 -> bf16 bit patterns, round to nearest even (NaNs stay NaNs)."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    rounded = (u + (np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1)))) >> np.uint32(16)
+    nan = (u & np.uint32(0x7FFFFFFF)) > np.uint32(0x7F800000)
+    return np.where(nan, (u >> np.uint32(16)) | np.uint32(0x40), rounded).astype(np.uint16)
+
+
 def _contig(shape) -> tuple:
     st, acc = [], 1
     for s in reversed(shape):

@@ -38,3 +38,21 @@ def test_config_table_is_described_without_a_gpu():
     cfgs = habu_b200.matmul_configs()
     assert len(cfgs) >= 3
     assert all(c.tile_m in (128, 256) and c.tile_k == 64 and c.stages >= 2 for c in cfgs)
+
+
+def test_product_package_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "habu_b200")
+    for name in os.listdir(pkg):
+        if name.endswith(".py"):
+            text = open(os.path.join(pkg, name)).read()
+            assert not re.search(r"^\s*(import|from)\s+oracle\b", text, flags=re.M), name
+
+
+def test_host_bf16_conversion_matches_the_oracle_bit_for_bit():
+    import numpy as np
+
+    import oracle
+    from habu_b200.model_ir import f32_to_bf16_bits
+    x = oracle.normal((50000,), 3, 0.0, 5.0)
+    x[:9] = [0.0, -0.0, np.inf, -np.inf, np.nan, 1.00390625, 1.01171875, 3.0e38, 1e-40]
+    assert np.array_equal(f32_to_bf16_bits(x), oracle.to_bf16_bits(x))

@@ -2,8 +2,9 @@
 and 2 tensor-parallel ranks against both the oracle and each other.
 
 Tolerances: against the oracle in bf16-storage mode (same rounding points) max-abs 2e-2
-plus one bf16 output rounding; against the pure-fp32 oracle the same bound is reported
-by the full-size check in bench.py's notes, here only the small configuration is run."""
+plus one bf16 output rounding; against the pure-fp32 oracle max-abs 4e-2 plus one output
+rounding (two layers of bf16 residual-stream roundings sit between the two).  The small
+configuration keeps the oracle's run time to seconds."""
 import numpy as np
 import pytest
 

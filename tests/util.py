@@ -25,7 +25,7 @@ def bf16_close(got, ref, atol=2e-2):
 
 def max_rel(a, ref, eps=1e-3):
     """|a-ref| / max(|ref|, eps*max|ref|): relative error with a floor so that entries
-    that cancel to ~0 are judged against the scale of the matrix."""
+    that cancel to ~0 are measured against the scale of the matrix."""
     ref = ref.astype(np.float64)
     floor = eps * float(np.max(np.abs(ref)))
     return float(np.max(np.abs(a.astype(np.float64) - ref) / np.maximum(np.abs(ref), floor)))
