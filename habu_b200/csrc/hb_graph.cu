@@ -169,9 +169,15 @@ extern "C" hb_status hb_graph_view(hb_graph* g, int32_t base, int64_t offset, in
     x.stride[i] = stride[i];
     extent += (shape[i] - 1) * stride[i];
   }
-  // bounds: the view must stay inside a densely stored base
-  if (b.kind != 0 && extent >= numel(g->tensors[root_of(g, base)]) && g->tensors[root_of(g, base)].kind == 1)
-    return hb_fail(g->ctx, HB_ERR_INVALID, "graph: view reaches past the end of tensor %d", base);
+  // bounds: a view of a planner-owned tensor must stay inside it (the extent of caller-owned
+  // memory is not known here)
+  {
+    int64_t abs_extent = extent;
+    int id = base;
+    while (g->tensors[id].kind == 2) { abs_extent += g->tensors[id].offset; id = g->tensors[id].base; }
+    if (g->tensors[id].kind == 1 && abs_extent >= numel(g->tensors[id]))
+      return hb_fail(g->ctx, HB_ERR_INVALID, "graph: view reaches past the end of tensor %d", base);
+  }
   x.base = base;
   x.offset = offset;
   g->tensors.push_back(x);

@@ -102,3 +102,16 @@ def test_side_stream_nodes_are_ordered_by_their_data(ctx):
     ref = ref + x
     assert bf16_close(oracle.from_bf16_bits(ctx.download(dout)), ref) < 0
     g.close()
+
+
+def test_view_past_the_end_of_a_planner_tensor_is_rejected(ctx):
+    g = Graph(ctx)
+    t = g.temp((16, 64))
+    ok = g.view(t, 64, (15, 64), (64, 1))
+    assert ok >= 0
+    with pytest.raises(hb.HabuError) as e:
+        g.view(t, 64, (16, 64), (64, 1))            # one row too many
+    assert e.value.status == 1
+    with pytest.raises(hb.HabuError):
+        g.view(ok, 64 * 14, (2, 64), (64, 1))       # nested view: offsets accumulate
+    g.close()
