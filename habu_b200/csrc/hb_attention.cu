@@ -26,13 +26,6 @@ namespace {
 
 using namespace hb;
 
-// ex2 that keeps its place relative to the token barriers around the exponential phase.
-__device__ __forceinline__ float ex2_ordered(float x) {
-  float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 constexpr int D = 128;           // head_dim
 constexpr int BQ = 128;          // query rows per tile (two tiles per CTA)
 constexpr int BKV = 128;         // keys per KV tile
@@ -249,22 +242,8 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     float l = 0.f;                              // running sum of exp2
     bool ok = true;
     const int n_mine = n_t[t];
-    // Ping-pong of the exponentials: the two warpgroups share each scheduler's MUFU pipe, and
-    // left alone they fall into step and halve each other's rate while the tensor core idles.
-    // A token (two named barriers, 256 threads each: 128 that wait + 128 that hand over) lets
-    // only one group at a time into its ex2 phase; the other does its load / max / store work
-    // or waits for its S tile meanwhile.  Group 1 hands group 0 the first turn, then turns
-    // alternate strictly, so a barrier never collects two hand-overs without a wait between.
-    // The token is used for the first n_common KV tiles, which both groups visit; a group with
-    // a tile of its own beyond that (the diagonal one of the later query tile) runs it freely.
-    const int n_common = min(n_t[0], n_t[1]);
-    const int bar_mine = 2 + t, bar_other = 2 + (t ^ 1);
-    auto hands_over = [&](int k) { return t == 0 ? k < n_common : k + 1 < n_common; };
-    if (t == 1 && n_common > 0) asm volatile("bar.arrive %0, 256;" ::"r"(bar_other) : "memory");
-    int j = 0;
-    for (; j < n_mine && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + t * 8, j & 1, abort_flag));
-      if (!ok) break;
+    for (int j = 0; j < n_mine && ok; ++j) {
+      if (!mbar_wait(bar_s_full + t * 8, j & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       uint32_t sv[128];
 #pragma unroll
@@ -313,7 +292,6 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
       }
       const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref * p.scale_log2;
-      if (j < n_common) asm volatile("bar.sync %0, 256;" ::"r"(bar_mine) : "memory");   // my turn on the MUFU pipes
       // P is produced and published in two halves of 64 keys: the PV product starts on the
       // first half while the second is still being exponentiated.
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
@@ -323,27 +301,20 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const int e = hf * 64 + 2 * i;
-          const float e0 = ex2_ordered(fmaf(__uint_as_float(sv[e]), p.scale_log2, neg_m));
-          const float e1 = ex2_ordered(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, neg_m));
-          const float e2 = ex2_ordered(fmaf(__uint_as_float(sv[e + 2]), p.scale_log2, neg_m));
-          const float e3 = ex2_ordered(fmaf(__uint_as_float(sv[e + 3]), p.scale_log2, neg_m));
+          const float e0 = ex2_approx(fmaf(__uint_as_float(sv[e]), p.scale_log2, neg_m));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(sv[e + 1]), p.scale_log2, neg_m));
+          const float e2 = ex2_approx(fmaf(__uint_as_float(sv[e + 2]), p.scale_log2, neg_m));
+          const float e3 = ex2_approx(fmaf(__uint_as_float(sv[e + 3]), p.scale_log2, neg_m));
           l0 += e0; l1 += e1; l2 += e2; l3 += e3;
           pk[i] = pack_bf16x2(e0, e1);
           pk[i + 1] = pack_bf16x2(e2, e3);
         }
-        if (hf == 1 && j < n_common && hands_over(j)) asm volatile("bar.arrive %0, 256;" ::"r"(bar_other) : "memory");
         tmem_st_32x32(tS + hf * 32, pk);     // 32 packed columns = 64 keys
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p_ready + (t * 2 + hf) * 8);
       }
       l += (l0 + l1) + (l2 + l3);
-    }
-    // Keep the token protocol whole: iterations skipped after a time-out still take and pass
-    // their turn, so the other group's waits stay matched.
-    for (int k = j; k < n_common; ++k) {
-      asm volatile("bar.sync %0, 256;" ::"r"(bar_mine) : "memory");
-      if (hands_over(k)) asm volatile("bar.arrive %0, 256;" ::"r"(bar_other) : "memory");
     }
     // ---- epilogue: O / l -> bf16 -> global
     if (ok && n_mine > 0) {
