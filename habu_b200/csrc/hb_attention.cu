@@ -445,17 +445,59 @@ extern "C" hb_status hb_attention_host(hb_ctx* ctx, const void* Q, const void* K
   char* dK = dQ + up(q_b);
   char* dV = dK + up(kv_b);
   char* dO = dV + up(kv_b);
-  if ((st = hb_upload(ctx, dQ, Q, q_b)) != HB_OK) return st;
-  if ((st = hb_upload(ctx, dK, K, kv_b)) != HB_OK) return st;
-  if ((st = hb_upload(ctx, dV, V, kv_b)) != HB_OK) return st;
-  auto mk = [&](void* ptr, int64_t heads) {
-    hb_tensor t = {ptr, HB_BF16, 4, {batch, seq, heads, head_dim},
+  const int64_t q_row = seq * n_q_heads * head_dim, kv_row = seq * n_kv_heads * head_dim;   // elements per batch entry
+  auto mk = [&](char* ptr, int64_t heads, int64_t b0, int64_t nb) {
+    hb_tensor t = {ptr + (size_t)b0 * seq * heads * head_dim * 2, HB_BF16, 4, {nb, seq, heads, head_dim},
                    {seq * heads * head_dim, heads * head_dim, head_dim, 1}};
     return t;
   };
-  hb_tensor tQ = mk(dQ, n_q_heads), tK = mk(dK, n_kv_heads), tV = mk(dV, n_kv_heads), tO = mk(dO, n_q_heads);
   hb_attn_opts opts = {causal, scale, nullptr, -1};
-  if ((st = hb_attention(ctx, &tQ, &tK, &tV, &tO, &opts)) != HB_OK) return st;
-  if ((st = hb_download(ctx, O, dO, q_b)) != HB_OK) return st;
+  // Batch entries are independent, so large calls are pipelined over groups of them: copy-in
+  // of group i+1 and copy-out of group i-1 run under the kernel of group i.
+  const int chunks = (batch >= 2 && q_b >= (size_t(8) << 20)) ? (int)(batch < 8 ? batch : 8) : 1;
+  if (chunks == 1) {
+    if ((st = hb_upload(ctx, dQ, Q, q_b)) != HB_OK) return st;
+    if ((st = hb_upload(ctx, dK, K, kv_b)) != HB_OK) return st;
+    if ((st = hb_upload(ctx, dV, V, kv_b)) != HB_OK) return st;
+    hb_tensor tQ = mk(dQ, n_q_heads, 0, batch), tK = mk(dK, n_kv_heads, 0, batch);
+    hb_tensor tV = mk(dV, n_kv_heads, 0, batch), tO = mk(dO, n_q_heads, 0, batch);
+    if ((st = hb_attention(ctx, &tQ, &tK, &tV, &tO, &opts)) != HB_OK) return st;
+    if ((st = hb_download(ctx, O, dO, q_b)) != HB_OK) return st;
+    return hb_sync(ctx);
+  }
+  cudaEvent_t* ev = nullptr;
+  if ((st = hb_host_pipe(ctx, 2 * chunks + 2, &ev)) != HB_OK) return st;
+  cudaEvent_t ev_start = ev[2 * chunks], ev_done = ev[2 * chunks + 1];
+  const int64_t per = (batch + chunks - 1) / chunks;
+  HB_CUDA(ctx, cudaEventRecord(ev_start, ctx->stream));
+  HB_CUDA(ctx, cudaStreamWaitEvent(ctx->h2d_stream, ev_start, 0));
+  HB_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ev_start, 0));
+  for (int i = 0; i < chunks; ++i) {
+    const int64_t b0 = i * per, nb = (b0 + per <= batch ? per : batch - b0);
+    if (nb <= 0) { HB_CUDA(ctx, cudaEventRecord(ev[i], ctx->h2d_stream)); continue; }
+    const size_t qo = (size_t)b0 * q_row * 2, ko = (size_t)b0 * kv_row * 2;
+    HB_CUDA(ctx, cudaMemcpyAsync(dQ + qo, static_cast<const char*>(Q) + qo, (size_t)nb * q_row * 2,
+                                 cudaMemcpyHostToDevice, ctx->h2d_stream));
+    HB_CUDA(ctx, cudaMemcpyAsync(dK + ko, static_cast<const char*>(K) + ko, (size_t)nb * kv_row * 2,
+                                 cudaMemcpyHostToDevice, ctx->h2d_stream));
+    HB_CUDA(ctx, cudaMemcpyAsync(dV + ko, static_cast<const char*>(V) + ko, (size_t)nb * kv_row * 2,
+                                 cudaMemcpyHostToDevice, ctx->h2d_stream));
+    HB_CUDA(ctx, cudaEventRecord(ev[i], ctx->h2d_stream));
+  }
+  for (int i = 0; i < chunks; ++i) {
+    const int64_t b0 = i * per, nb = (b0 + per <= batch ? per : batch - b0);
+    if (nb <= 0) continue;
+    HB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ev[i], 0));
+    hb_tensor tQ = mk(dQ, n_q_heads, b0, nb), tK = mk(dK, n_kv_heads, b0, nb);
+    hb_tensor tV = mk(dV, n_kv_heads, b0, nb), tO = mk(dO, n_q_heads, b0, nb);
+    if ((st = hb_attention(ctx, &tQ, &tK, &tV, &tO, &opts)) != HB_OK) return st;
+    HB_CUDA(ctx, cudaEventRecord(ev[chunks + i], ctx->stream));
+    HB_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ev[chunks + i], 0));
+    const size_t qo = (size_t)b0 * q_row * 2;
+    HB_CUDA(ctx, cudaMemcpyAsync(static_cast<char*>(O) + qo, dO + qo, (size_t)nb * q_row * 2,
+                                 cudaMemcpyDeviceToHost, ctx->d2h_stream));
+  }
+  HB_CUDA(ctx, cudaEventRecord(ev_done, ctx->d2h_stream));
+  HB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ev_done, 0));
   return hb_sync(ctx);
 }

@@ -44,6 +44,10 @@ struct hb_ctx {
   cudaStream_t own_stream = nullptr;  // created by the context
   cudaStream_t side_stream = nullptr; // second stream for executor nodes that overlap (collectives)
   cudaEvent_t side_event = nullptr;   // fork / join marker between the two streams
+  // host-buffer entry points: copy-in and copy-out streams and a pool of ordering events, so
+  // that PCIe transfers in both directions overlap the kernels chunk by chunk
+  cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+  std::vector<cudaEvent_t> event_pool;
   int32_t* d_status = nullptr;
   int32_t* h_status = nullptr;        // pinned
   int* d_tickets = nullptr;           // split-K arrival tickets, one per output tile, zero between launches
@@ -67,8 +71,15 @@ struct hb_ctx {
 
 hb_status hb_fail(hb_ctx* ctx, hb_status code, const char* fmt, ...);
 hb_status hb_check_cuda(hb_ctx* ctx, cudaError_t e, const char* what);
+#define HB_CUDA(ctx, call)                                        \
+  do {                                                            \
+    cudaError_t e__ = (call);                                     \
+    if (e__ != cudaSuccess) return hb_check_cuda(ctx, e__, #call); \
+  } while (0)
 // Grow-only scratch buffer `slot` on the context's device.
 hb_status hb_get_scratch(hb_ctx* ctx, int slot, size_t bytes, void** out);
+// Copy streams and `n` ordering events for the pipelined host-buffer entry points.
+hb_status hb_host_pipe(hb_ctx* ctx, int n, cudaEvent_t** events);
 
 // cuTensorMapEncodeTiled fetched through the runtime (no link against libcuda).
 // dims/strides innermost first; strides in bytes for dims 1..rank-1.

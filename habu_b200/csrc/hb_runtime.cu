@@ -21,12 +21,6 @@ hb_status hb_check_cuda(hb_ctx* ctx, cudaError_t e, const char* what) {
   return hb_fail(ctx, HB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
-#define HB_CUDA(ctx, call)                                        \
-  do {                                                            \
-    cudaError_t e__ = (call);                                     \
-    if (e__ != cudaSuccess) return hb_check_cuda(ctx, e__, #call); \
-  } while (0)
-
 extern "C" hb_status hb_ctx_create(int32_t device, hb_ctx** out) {
   if (!out) return HB_ERR_INVALID;
   *out = nullptr;
@@ -66,6 +60,9 @@ extern "C" hb_status hb_ctx_destroy(hb_ctx* ctx) {
   if (ctx->d_tickets) cudaFree(ctx->d_tickets);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  for (cudaEvent_t e : ctx->event_pool) cudaEventDestroy(e);
+  if (ctx->h2d_stream) cudaStreamDestroy(ctx->h2d_stream);
+  if (ctx->d2h_stream) cudaStreamDestroy(ctx->d2h_stream);
   if (ctx->side_event) cudaEventDestroy(ctx->side_event);
   if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -277,6 +274,23 @@ extern "C" hb_status hb_matmul(hb_ctx* ctx, const hb_tensor* A, const hb_tensor*
   return hb_launch_gemm_bf16(ctx, g, cfg);
 }
 
+hb_status hb_host_pipe(hb_ctx* ctx, int n, cudaEvent_t** events) {
+  HB_CUDA(ctx, cudaSetDevice(ctx->device));
+  if (!ctx->h2d_stream) HB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+  if (!ctx->d2h_stream) HB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+  while ((int)ctx->event_pool.size() < n) {
+    cudaEvent_t e;
+    HB_CUDA(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    ctx->event_pool.push_back(e);
+  }
+  *events = ctx->event_pool.data();
+  return HB_OK;
+}
+
+// Host-buffer matmul.  Large bf16 products are pipelined in row chunks over three streams:
+// copy-in (B, then the A chunks), compute (one matmul per chunk as soon as its rows have
+// landed) and copy-out (each C chunk as soon as it is computed), so the PCIe transfers in
+// both directions run under each other and under the kernels.
 extern "C" hb_status hb_matmul_host(hb_ctx* ctx, const void* A_host, const void* B_host, void* C_host,
                                     int64_t M, int64_t N, int64_t K, int32_t dtype) {
   if (!ctx) return HB_ERR_INVALID;
@@ -292,12 +306,44 @@ extern "C" hb_status hb_matmul_host(hb_ctx* ctx, const void* A_host, const void*
   char* dA = static_cast<char*>(base);
   char* dB = dA + up(a_b);
   char* dC = dB + up(b_b);
-  if ((st = hb_upload(ctx, dA, A_host, a_b)) != HB_OK) return st;
-  if ((st = hb_upload(ctx, dB, B_host, b_b)) != HB_OK) return st;
-  hb_tensor tA = {dA, dtype, 2, {M, K, 0, 0}, {K, 1, 0, 0}};
-  hb_tensor tB = {dB, dtype, 2, {K, N, 0, 0}, {1, K, 0, 0}};
-  hb_tensor tC = {dC, dtype, 2, {M, N, 0, 0}, {N, 1, 0, 0}};
-  if ((st = hb_matmul(ctx, &tA, &tB, &tC, nullptr)) != HB_OK) return st;
-  if ((st = hb_download(ctx, C_host, dC, c_b)) != HB_OK) return st;
+  const int chunks = (dtype == HB_BF16 && M >= 2048 && M % 1024 == 0) ? 4 : 1;
+  if (chunks == 1) {
+    if ((st = hb_upload(ctx, dA, A_host, a_b)) != HB_OK) return st;
+    if ((st = hb_upload(ctx, dB, B_host, b_b)) != HB_OK) return st;
+    hb_tensor tA = {dA, dtype, 2, {M, K, 0, 0}, {K, 1, 0, 0}};
+    hb_tensor tB = {dB, dtype, 2, {K, N, 0, 0}, {1, K, 0, 0}};
+    hb_tensor tC = {dC, dtype, 2, {M, N, 0, 0}, {N, 1, 0, 0}};
+    if ((st = hb_matmul(ctx, &tA, &tB, &tC, nullptr)) != HB_OK) return st;
+    if ((st = hb_download(ctx, C_host, dC, c_b)) != HB_OK) return st;
+    return hb_sync(ctx);
+  }
+  cudaEvent_t* ev = nullptr;
+  if ((st = hb_host_pipe(ctx, 2 * chunks + 2, &ev)) != HB_OK) return st;
+  cudaEvent_t ev_start = ev[2 * chunks], ev_done = ev[2 * chunks + 1];
+  const int64_t rows = M / chunks;
+  HB_CUDA(ctx, cudaEventRecord(ev_start, ctx->stream));          // copies start after earlier work
+  HB_CUDA(ctx, cudaStreamWaitEvent(ctx->h2d_stream, ev_start, 0));
+  HB_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ev_start, 0));
+  HB_CUDA(ctx, cudaMemcpyAsync(dB, B_host, b_b, cudaMemcpyHostToDevice, ctx->h2d_stream));
+  for (int i = 0; i < chunks; ++i) {
+    const size_t off = (size_t)i * rows * K * es;
+    HB_CUDA(ctx, cudaMemcpyAsync(dA + off, static_cast<const char*>(A_host) + off, (size_t)rows * K * es,
+                                 cudaMemcpyHostToDevice, ctx->h2d_stream));
+    HB_CUDA(ctx, cudaEventRecord(ev[i], ctx->h2d_stream));
+  }
+  for (int i = 0; i < chunks; ++i) {
+    HB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ev[i], 0));
+    hb_tensor tA = {dA + (size_t)i * rows * K * es, dtype, 2, {rows, K, 0, 0}, {K, 1, 0, 0}};
+    hb_tensor tB = {dB, dtype, 2, {K, N, 0, 0}, {1, K, 0, 0}};
+    hb_tensor tC = {dC + (size_t)i * rows * N * es, dtype, 2, {rows, N, 0, 0}, {N, 1, 0, 0}};
+    if ((st = hb_matmul(ctx, &tA, &tB, &tC, nullptr)) != HB_OK) return st;
+    HB_CUDA(ctx, cudaEventRecord(ev[chunks + i], ctx->stream));
+    HB_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ev[chunks + i], 0));
+    const size_t coff = (size_t)i * rows * N * es;
+    HB_CUDA(ctx, cudaMemcpyAsync(static_cast<char*>(C_host) + coff, dC + coff, (size_t)rows * N * es,
+                                 cudaMemcpyDeviceToHost, ctx->d2h_stream));
+  }
+  HB_CUDA(ctx, cudaEventRecord(ev_done, ctx->d2h_stream));
+  HB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ev_done, 0));
   return hb_sync(ctx);
 }

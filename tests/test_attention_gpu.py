@@ -111,6 +111,25 @@ def test_full_size_config_sampled_heads(ctx):
         ctx.free(t)
 
 
+def test_host_entry_point_pipelines_batch_groups(ctx):
+    # 10 batch entries go through the host call as 5 groups of 2 over the copy-in, compute and
+    # copy-out streams; grouped-query heads; the result equals the one-launch device call
+    B, S, HQ, HKV, D = 10, 512, 8, 2, 128
+    Q, Qb = bf16_normal((B, S, HQ, D), SEED + 61)
+    K, Kb = bf16_normal((B, S, HKV, D), SEED + 62)
+    V, Vb = bf16_normal((B, S, HKV, D), SEED + 63)
+    dQ, dK, dV = ctx.upload(Qb), ctx.upload(Kb), ctx.upload(Vb)
+    dO = ctx.attention(dQ, dK, dV)
+    ctx.sync()
+    got = ctx.download(dO)
+    for _ in range(2):
+        assert np.array_equal(ctx.attention_host(Qb, Kb, Vb), got)
+    sl = lambda X: np.ascontiguousarray(X[9:10])
+    assert max_abs(oracle.from_bf16_bits(got[9:10]), oracle.attention(sl(Q), sl(K), sl(V))) < TOL
+    for t in (dQ, dK, dV, dO):
+        ctx.free(t)
+
+
 def test_invalid_arguments(ctx):
     q = ctx.empty((1, 128, 3, 128))
     k = ctx.empty((1, 128, 2, 128))

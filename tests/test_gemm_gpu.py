@@ -118,6 +118,18 @@ def test_bf16_linearity_property_full_size(ctx):
         ctx.free(t)
 
 
+def test_host_entry_point_pipelines_row_chunks(ctx):
+    # M >= 2048 goes through the host call as four row chunks over the copy-in, compute and
+    # copy-out streams; two calls in a row reuse the staging buffer and the events
+    M, N, K = 2048, 264, 136
+    A, Ab = bf16_normal((M, K), SEED + 15, K ** -0.5)
+    Bt, Btb = bf16_normal((N, K), SEED + 16)
+    ref = oracle.gemm(A, Bt.T)
+    for _ in range(2):
+        host = oracle.from_bf16_bits(ctx.matmul_host(Ab, Btb))
+        assert max_abs(host, ref) < TOL_BF16
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 256, 256), (100, 37, 50), (1, 1, 1)])
 def test_f32_path(ctx, M, N, K):
     A = oracle.uniform((M, K), SEED + 21)
