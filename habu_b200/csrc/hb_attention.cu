@@ -116,8 +116,8 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + t * 8, 1);
-      mbar_init(bar_p_ready + (t * 2) * 8, 128);
-      mbar_init(bar_p_ready + (t * 2 + 1) * 8, 128);
+      mbar_init(bar_p_ready + (t * 2) * 8, 4);        // one arrival per softmax warp of the tile
+      mbar_init(bar_p_ready + (t * 2 + 1) * 8, 4);
       mbar_init(bar_o_full + t * 8, 1);
     }
     mbar_fence_init();
@@ -163,16 +163,20 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       const uint32_t idesc_qk = umma_idesc_bf16(BQ, BKV, 0, 0);
       const uint32_t idesc_pv = umma_idesc_bf16(BQ, D, 0, 1);
       bool ok = true;
+      // Descriptors are built once; inside the loops only the 14-bit start-address field
+      // (bytes >> 4, in the low word) moves, by constants that cannot carry out of it.
+      const uint64_t desc_q = umma_desc_k_sw128(sQ);
+      const uint64_t desc_k = umma_desc_k_sw128(sK);
+      const uint64_t desc_v = umma_desc_mn_sw128(sV, HALF_BYTES, 1024);
       auto issue_qk = [&](int t, int j) {
         const int s = j % KV_STAGES;
         const uint32_t d_tmem = tmem_base + t * 128;
-        const uint32_t a_addr = sQ + t * TILE_BYTES;
-        const uint32_t b_addr = sK + s * TILE_BYTES;
+        const uint64_t a_desc = desc_q + static_cast<uint32_t>(t * (TILE_BYTES >> 4));
+        const uint64_t b_desc = desc_k + static_cast<uint32_t>(s * (TILE_BYTES >> 4));
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          umma_ss<1>(d_tmem, umma_desc_k_sw128(a_addr + off), umma_desc_k_sw128(b_addr + off), idesc_qk,
-                     kk != 0 ? 1u : 0u);
+          const uint32_t off = ((kk >> 2) * HALF_BYTES + (kk & 3) * 32) >> 4;
+          umma_ss<1>(d_tmem, a_desc + off, b_desc + off, idesc_qk, kk != 0 ? 1u : 0u);
         }
         umma_commit<1>(bar_s_full + t * 8);
       };
@@ -180,10 +184,10 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         const int s = j % KV_STAGES;
         const uint32_t d_tmem = tmem_base + 256 + t * 128;
         const uint32_t a_tmem = tmem_base + t * 128;     // P aliases S: 64 packed columns
-        const uint32_t b_addr = sV + s * TILE_BYTES;
+        const uint64_t b_desc = desc_v + static_cast<uint32_t>(s * (TILE_BYTES >> 4));
 #pragma unroll
         for (int kk = hf * 4; kk < hf * 4 + 4; ++kk)
-          umma_ts(d_tmem, a_tmem + kk * 8, umma_desc_mn_sw128(b_addr + kk * 2048, HALF_BYTES, 1024), idesc_pv,
+          umma_ts(d_tmem, a_tmem + kk * 8, b_desc + static_cast<uint32_t>(kk * (2048 >> 4)), idesc_pv,
                   (j | kk) != 0 ? 1u : 0u);
       };
       if (!mbar_wait(bar_q_full, 0, abort_flag)) ok = false;
@@ -202,26 +206,19 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         const uint32_t ph = (j / KV_STAGES) & 1;
         const int sn = (j + 1) % KV_STAGES;
         const uint32_t phn = ((j + 1) / KV_STAGES) & 1;
-        bool k_next_waited = false;
         if (!mbar_wait(bar_v_full + s * 8, ph, abort_flag)) { ok = false; break; }
+        if (j + 1 < n_max && !mbar_wait(bar_k_full + sn * 8, phn, abort_flag)) { ok = false; break; }
         for (int t = 0; t < 2; ++t) {
           if (j < n_t[t]) {
-            if (!mbar_wait(bar_p_ready + (t * 2) * 8, j & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_spin(bar_p_ready + (t * 2) * 8, j & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             issue_pv(t, j, 0);
-            if (!mbar_wait(bar_p_ready + (t * 2 + 1) * 8, j & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_spin(bar_p_ready + (t * 2 + 1) * 8, j & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             issue_pv(t, j, 1);
             if (j + 1 == n_t[t]) umma_commit<1>(bar_o_full + t * 8);
           }
-          if (j + 1 < n_t[t]) {
-            if (!k_next_waited) {
-              if (!mbar_wait(bar_k_full + sn * 8, phn, abort_flag)) { ok = false; break; }
-              tc_fence_after();
-              k_next_waited = true;
-            }
-            issue_qk(t, j + 1);
-          }
+          if (j + 1 < n_t[t]) issue_qk(t, j + 1);
         }
         if (!ok) break;
         umma_commit<1>(bar_v_empty + s * 8);
@@ -312,7 +309,8 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         tmem_st_32x32(tS + hf * 32, pk);     // 32 packed columns = 64 keys
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(bar_p_ready + (t * 2 + hf) * 8);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p_ready + (t * 2 + hf) * 8);
       }
       l += (l0 + l1) + (l2 + l3);
     }

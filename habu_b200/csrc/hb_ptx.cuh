@@ -89,6 +89,33 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   return false;
 }
 
+// Non-suspending variant: polls with test_wait, so the waiter reacts within a few cycles of
+// the phase completing.  For warps that have nothing else to run beside them.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity,
+                                               volatile int* abort_flag) {
+  for (uint32_t i = 0; i < HB_SPIN_LIMIT * 16u; ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 4095u) == 4095u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+// Named barrier over `count` threads (a multiple of 32); id 0 is __syncthreads().
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 // ---------------------------------------------------------------- cluster helpers
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
