@@ -240,7 +240,7 @@ class DecoderWorkload:
     """Llama-style decoder block forward x2 layers, bf16, tensor-parallel over all ranks:
     d_model 4096, 32 query / 8 KV heads, head_dim 128, SwiGLU hidden 14336, batch 4 x seq 2048."""
     bound = "tensor"
-    kernel = "hb_gemm_bf16_kernel"
+    kernel = "hb_gemm_bf16_pair_kernel"     # dominant kernel of the step (projections and FFN products)
     flush = None
     scaling = "strong"
     collective = True
@@ -326,7 +326,7 @@ class MlpWorkload:
     """4-layer MLP forward + backward + Adam, width 8192, GELU, batch 4096 per GPU, MSE; bf16
     activations / gradients, fp32 master weights and moments; data-parallel gradient allreduce."""
     bound = "tensor"
-    kernel = "hb_gemm_bf16_kernel"
+    kernel = "hb_gemm_bf16_pair_kernel"     # dominant kernel of the step (forward and both backward products)
     flush = None
     scaling = "weak"
     collective = True
