@@ -111,10 +111,6 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity,
   *abort_flag = 1;
   return false;
 }
-// Named barrier over `count` threads (a multiple of 32); id 0 is __syncthreads().
-__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
 
 // ---------------------------------------------------------------- cluster helpers
 __device__ __forceinline__ uint32_t cluster_ctarank() {
