@@ -106,6 +106,8 @@ def load() -> C.CDLL:
         "hb_graph_view": [vp, i32, i64, i32, C.POINTER(i64), C.POINTER(i64), C.POINTER(i32)],
         "hb_graph_add": [vp, C.POINTER(hb_node)],
         "hb_graph_plan": [vp, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
+        "hb_plan_arena": [i32, C.POINTER(C.c_size_t), C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_size_t),
+                          C.POINTER(C.c_size_t)],
         "hb_graph_run": [vp],
         "hb_graph_run_timed": [vp, C.POINTER(C.c_float), i32],
         "hb_graph_describe": [vp, C.c_char_p, C.c_size_t],

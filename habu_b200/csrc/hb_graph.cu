@@ -202,6 +202,44 @@ extern "C" hb_status hb_graph_add(hb_graph* g, const hb_node* n) {
   return HB_OK;
 }
 
+// Arena placement by lifetime: buffers are taken largest first (ties by index) and each goes to
+// the lowest 256-byte-aligned offset that is free during its whole lifetime [first, last]
+// (node indices, inclusive).  Pure host arithmetic; the executor calls it once per arena.
+extern "C" hb_status hb_plan_arena(int32_t n, const size_t* bytes, const int32_t* first, const int32_t* last,
+                                   size_t* offsets, size_t* total) {
+  if (n < 0 || !total || (n > 0 && (!bytes || !first || !last || !offsets))) return HB_ERR_INVALID;
+  for (int i = 0; i < n; ++i)
+    if (first[i] < 0 || last[i] < first[i]) return HB_ERR_INVALID;
+  auto up = [](size_t x) { return (x + 255) & ~size_t(255); };
+  std::vector<int> order(n);
+  for (int i = 0; i < n; ++i) order[i] = i;
+  std::sort(order.begin(), order.end(), [&](int a, int b) {
+    if (bytes[a] != bytes[b]) return bytes[a] > bytes[b];
+    return a < b;
+  });
+  std::vector<int> placed;
+  size_t top = 0;
+  for (int id : order) {
+    const size_t sz = up(bytes[id]);
+    std::vector<std::pair<size_t, size_t>> busy;   // [begin, end) of the buffers alive at the same time
+    for (int o : placed) {
+      if (last[o] < first[id] || last[id] < first[o]) continue;
+      busy.emplace_back(offsets[o], offsets[o] + up(bytes[o]));
+    }
+    std::sort(busy.begin(), busy.end());
+    size_t off = 0;
+    for (const auto& b : busy) {
+      if (off + sz <= b.first) break;
+      if (b.second > off) off = b.second;
+    }
+    offsets[id] = off;
+    placed.push_back(id);
+    if (off + sz > top) top = off + sz;
+  }
+  *total = top;
+  return HB_OK;
+}
+
 extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* symmetric_bytes) {
   if (!g) return HB_ERR_INVALID;
   hb_ctx* ctx = g->ctx;
@@ -245,31 +283,18 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
       const bool sym = (t.flags & HB_T_SYMMETRIC) != 0;
       if ((int)sym == pass) ids.push_back(i);
     }
-    std::sort(ids.begin(), ids.end(), [&](int a, int b) {
-      if (g->tensors[a].bytes != g->tensors[b].bytes) return g->tensors[a].bytes > g->tensors[b].bytes;
-      return a < b;
-    });
-    std::vector<int> placed;
-    for (int id : ids) {
-      hb_graph_tensor& t = g->tensors[id];
-      const size_t sz = (t.bytes + 255) & ~size_t(255);
-      // candidate offsets: 0 and the end of every conflicting tensor
-      std::vector<std::pair<size_t, size_t>> busy;   // [begin, end) of time-overlapping tensors
-      for (int o : placed) {
-        const hb_graph_tensor& u = g->tensors[o];
-        if (u.last < t.first || t.last < u.first) continue;
-        busy.emplace_back(u.arena_off, u.arena_off + ((u.bytes + 255) & ~size_t(255)));
-      }
-      std::sort(busy.begin(), busy.end());
-      size_t off = 0;
-      for (const auto& b : busy) {
-        if (off + sz <= b.first) break;
-        if (b.second > off) off = b.second;
-      }
-      t.arena_off = off;
-      t.in_symmetric = pass == 1;
-      placed.push_back(id);
-      if (off + sz > totals[pass]) totals[pass] = off + sz;
+    std::vector<size_t> bytes(ids.size()), offs(ids.size());
+    std::vector<int32_t> first(ids.size()), last(ids.size());
+    for (size_t k = 0; k < ids.size(); ++k) {
+      bytes[k] = g->tensors[ids[k]].bytes;
+      first[k] = g->tensors[ids[k]].first;
+      last[k] = g->tensors[ids[k]].last;
+    }
+    hb_status st = hb_plan_arena((int32_t)ids.size(), bytes.data(), first.data(), last.data(), offs.data(), &totals[pass]);
+    if (st != HB_OK) return hb_fail(ctx, st, "graph: arena planning failed");
+    for (size_t k = 0; k < ids.size(); ++k) {
+      g->tensors[ids[k]].arena_off = offs[k];
+      g->tensors[ids[k]].in_symmetric = pass == 1;
     }
   }
   // symmetric tensors fall back to the ordinary arena when no peer buffer can hold them

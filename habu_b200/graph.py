@@ -127,3 +127,21 @@ class Graph:
         self.ctx._check(_lib.hb_graph_tensor_ptr(self._h, i, C.byref(p)))
         dtype, shape, stride = self.meta[i]
         return Tensor(p.value, dtype, shape, stride)
+
+
+def plan_arena(sizes: Sequence[int], first: Sequence[int], last: Sequence[int]):
+    """The executor's placement rule on its own (``hb_plan_arena``; host arithmetic, needs no
+    GPU): returns (offsets, total_bytes) for buffers of ``sizes[i]`` bytes alive over node
+    indices ``[first[i], last[i]]``."""
+    n = len(sizes)
+    if not (len(first) == len(last) == n):
+        raise ValueError("sizes, first and last must have the same length")
+    b = (C.c_size_t * n)(*sizes)
+    f = (C.c_int32 * n)(*first)
+    l = (C.c_int32 * n)(*last)
+    offs = (C.c_size_t * n)()
+    total = C.c_size_t(0)
+    st = _lib.hb_plan_arena(n, b, f, l, offs, C.byref(total))
+    if st != 0:
+        raise ValueError(f"hb_plan_arena: status {st}")
+    return list(offs), total.value

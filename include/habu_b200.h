@@ -258,6 +258,12 @@ hb_status hb_graph_view(hb_graph* g, int32_t base, int64_t offset, int32_t rank,
                         const int64_t* shape, const int64_t* stride, int32_t* id);
 hb_status hb_graph_add(hb_graph* g, const hb_node* node);
 hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* symmetric_bytes);
+/* The planner's placement rule on its own (host arithmetic only, needs no context or GPU):
+ * `n` buffers of `bytes[i]` alive over node indices [first[i], last[i]] are packed largest
+ * first, each at the lowest 256-byte-aligned offset free during its lifetime.  No reference
+ * counterpart (the reference allocates nothing on a device). */
+hb_status hb_plan_arena(int32_t n, const size_t* bytes, const int32_t* first, const int32_t* last,
+                        size_t* offsets, size_t* total);
 hb_status hb_graph_run(hb_graph* g);
 /* One run with a CUDA event between nodes: ms[i] = device time of node i (first n nodes). */
 hb_status hb_graph_run_timed(hb_graph* g, float* ms, int32_t n);
