@@ -51,6 +51,11 @@ class hb_tune_result(C.Structure):
                 ("tflops", C.c_float)]
 
 
+class hb_matmul_route(C.Structure):
+    _fields_ = [("kernel", C.c_int32), ("config_id", C.c_int32), ("grid", C.c_int32), ("tiles", C.c_int32),
+                ("max_segments", C.c_int32), ("scratch_bytes", C.c_int64)]
+
+
 class hb_node(C.Structure):
     _fields_ = [("kind", C.c_int32), ("inputs", C.c_int32 * 4), ("out", C.c_int32),
                 ("iparam", C.c_int32 * 4), ("fparam", C.c_float * 2), ("stream", C.c_int32)]
@@ -115,6 +120,7 @@ def load() -> C.CDLL:
         "hb_autotune": [vp, C.POINTER(hb_op_desc), i32, C.POINTER(hb_tune_result)],
         "hb_tune_cache_load": [vp, C.c_char_p],
         "hb_tune_cache_save": [vp, C.c_char_p],
+        "hb_matmul_default_route": [i32, C.POINTER(hb_op_desc), C.POINTER(hb_matmul_route)],
         "hb_matmul_config_info": [i32, C.POINTER(hb_tune_result)],
     }
     for name, args in sigs.items():

@@ -11,6 +11,7 @@
 int hb_gemm_num_configs();
 void hb_gemm_config_describe(int id, hb_tune_result* out);
 bool hb_gemm_config_supports(int id, const hb_gemm_args& a);
+int hb_gemm_heuristic_config(int sm_count, int64_t M, int64_t N);
 
 namespace {
 
@@ -46,26 +47,58 @@ int hb_gemm_pick_config(hb_ctx* ctx, const hb_gemm_args& a) {
   auto it = ctx->tune_cache.find(hb_tune_key(d, ctx->sm_count, ctx->world));
   if (it != ctx->tune_cache.end() && it->second.config_id < hb_gemm_num_configs())
     return it->second.config_id;
-  // Heuristic: the CTA-pair 256 x 256 tile when there is a tile for every pair of SMs; else the widest one-CTA tile that still gives every SM a tile.
+  return hb_gemm_heuristic_config(ctx->sm_count, a.M, a.N);
+}
+
+// The CTA-pair 256 x 256 tile when there is a tile for every pair of SMs; else the widest
+// one-CTA tile that still gives every SM a tile.
+int hb_gemm_heuristic_config(int sm_count, int64_t M, int64_t N) {
   const int n = hb_gemm_num_configs();
-  if (((a.M + 255) / 256) * ((a.N + 255) / 256) >= ctx->sm_count / 2) {
+  if (((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2) {
     for (int id = 0; id < n; ++id) {
       hb_tune_result r;
       hb_gemm_config_describe(id, &r);
       if (r.cluster == 2 && r.raster_group == 8) return id;
     }
   }
-  const int64_t tiles_m = (a.M + 127) / 128;
+  const int64_t tiles_m = (M + 127) / 128;
   int best = 0;
   for (int id = 0; id < n; ++id) {
     hb_tune_result r;
     hb_gemm_config_describe(id, &r);
     if (r.raster_group != 8 || r.cluster != 1) continue;
-    const int64_t tiles = tiles_m * ((a.N + r.tile_n - 1) / r.tile_n);
+    const int64_t tiles = tiles_m * ((N + r.tile_n - 1) / r.tile_n);
     best = id;
-    if (tiles >= ctx->sm_count) break;
+    if (tiles >= sm_count) break;
   }
   return best;
+}
+
+extern "C" hb_status hb_matmul_default_route(int32_t sm_count, const hb_op_desc* desc, hb_matmul_route* out) {
+  if (!desc || !out || sm_count < 1) return HB_ERR_INVALID;
+  if (desc->op != HB_OP_MATMUL || desc->dtype != HB_BF16) return HB_ERR_UNSUPPORTED;
+  if (desc->m <= 0 || desc->n <= 0 || desc->k <= 0) return HB_ERR_INVALID;
+  memset(out, 0, sizeof(*out));
+  hb_gemm_args a;
+  memset(&a, 0, sizeof(a));
+  a.M = desc->m; a.N = desc->n; a.K = desc->k;
+  a.a_mn_major = desc->layout & 1; a.b_mn_major = (desc->layout >> 1) & 1;
+  a.epilogue = desc->epilogue;
+  if (hb_gemm_skinny_applicable(a)) {
+    int grid = 0, max_seg = 0, tiles = 0;
+    size_t floats = 0;
+    hb_gemm_skinny_plan(sm_count, a.M, a.N, a.K, &grid, &max_seg, &floats, &tiles);
+    out->kernel = 2;
+    out->config_id = -1;
+    out->grid = grid; out->tiles = tiles; out->max_segments = max_seg;
+    out->scratch_bytes = (int64_t)(floats * sizeof(float));
+    return HB_OK;
+  }
+  hb_tune_result r;
+  out->config_id = hb_gemm_heuristic_config(sm_count, a.M, a.N);
+  hb_gemm_config_describe(out->config_id, &r);
+  out->kernel = r.cluster == 2 ? 1 : 0;
+  return HB_OK;
 }
 
 extern "C" int32_t hb_matmul_config_count(void) { return hb_gemm_num_configs(); }

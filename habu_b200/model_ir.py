@@ -348,3 +348,14 @@ def matmul_configs():
         _lib.hb_matmul_config_info(i, C.byref(r))
         out.append(r)
     return out
+
+
+def matmul_default_route(m: int, n: int, k: int, layout: int = 0, epilogue: int = HB_EPI_NONE, sm_count: int = 148):
+    """Kernel and configuration the dispatcher picks for a bf16 matmul that has no autotune
+    cache entry (``hb_matmul_default_route``; host arithmetic, needs no GPU)."""
+    d = _capi.hb_op_desc(0, HB_BF16, m, n, k, layout, epilogue)
+    r = _capi.hb_matmul_route()
+    st = _lib.hb_matmul_default_route(sm_count, C.byref(d), C.byref(r))
+    if st != 0:
+        raise ValueError(f"hb_matmul_default_route: status {st}")
+    return r

@@ -294,6 +294,20 @@ hb_status hb_tune_cache_load(hb_ctx* ctx, const char* path);
 hb_status hb_tune_cache_save(hb_ctx* ctx, const char* path);
 int32_t hb_matmul_config_count(void);
 hb_status hb_matmul_config_info(int32_t config_id, hb_tune_result* out);
+/* Where the dispatcher sends a bf16 matmul when the autotune cache has no entry for it
+ * (host arithmetic only, needs no context or GPU): `kernel` 0 = one-CTA tile kernel,
+ * 1 = CTA-pair 256 x 256 tile kernel, 2 = stream-K kernel for M <= 64; `config_id` for
+ * kernels 0 and 1; for kernel 2 the persistent grid, the column tiles, the most K ranges
+ * that can share a tile and the fp32 scratch the launch uses. */
+typedef struct hb_matmul_route {
+  int32_t kernel;
+  int32_t config_id;
+  int32_t grid;
+  int32_t tiles;
+  int32_t max_segments;
+  int64_t scratch_bytes;
+} hb_matmul_route;
+hb_status hb_matmul_default_route(int32_t sm_count, const hb_op_desc* desc, hb_matmul_route* out);
 
 #ifdef __cplusplus
 }

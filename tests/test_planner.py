@@ -72,3 +72,39 @@ def test_degenerate_inputs():
         plan_arena([16], [3], [2])          # dies before it is born
     with pytest.raises(ValueError):
         plan_arena([16], [-1], [2])
+
+
+# ---- default routing of bf16 matmuls (host arithmetic of the dispatcher)
+def test_default_route_of_the_configured_shapes():
+    from habu_b200.model_ir import matmul_default_route, matmul_configs
+    cfgs = matmul_configs()
+    for s in (4096, 8192):                       # a 256 x 256 tile for every pair of SMs: CTA-pair kernel
+        r = matmul_default_route(s, s, s)
+        assert r.kernel == 1 and cfgs[r.config_id].cluster == 2 and cfgs[r.config_id].tile_m == 256
+    r = matmul_default_route(1024, 1024, 1024)   # 16 pair tiles for 74 pairs: one-CTA tiles instead
+    assert r.kernel == 0 and cfgs[r.config_id].cluster == 1
+    assert (1024 // 128) * (1024 // cfgs[r.config_id].tile_n) >= 64
+    # M-major or N-major operands and fused epilogues never take the stream-K path
+    assert matmul_default_route(16, 8192, 8192, layout=2).kernel != 2
+    assert matmul_default_route(16, 8192, 8192, epilogue=1).kernel != 2
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 8192, 8192), (1, 256, 512), (7, 1000, 1096), (33, 4096, 2048), (64, 384, 8192),
+                                   (64, 128 * 1024, 64)])
+def test_stream_k_plan_covers_the_work_within_its_scratch(m, n, k):
+    from habu_b200.model_ir import matmul_default_route
+    r = matmul_default_route(m, n, k)
+    assert r.kernel == 2 and r.config_id == -1
+    tiles = -(-n // 128)
+    assert r.tiles == tiles
+    assert 1 <= r.grid <= 148
+    assert 2 <= r.max_segments <= max(2, r.grid)
+    mpad = -(-m // 16) * 16
+    assert r.scratch_bytes == tiles * r.max_segments * 128 * mpad * 4
+    # a K range never spans more tiles than the segments reserved for one tile allow:
+    # with `units` (tile, k-group) pairs dealt out evenly, a CTA's range is at least units // grid long
+    k_groups = -(-k // 128)
+    units = tiles * k_groups
+    shortest = units // r.grid
+    assert shortest >= 1
+    assert -(-k_groups // shortest) + 1 <= r.max_segments or r.max_segments == r.grid
