@@ -411,17 +411,20 @@ def run_reference(args, rank, world):
     import oracle
     oracle.use_all_cores()
     wl = WORKLOADS[args.workload]()
-    vals = []
+    vals, times = [], []
     sample = ""
     for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
         v, sample = wl.cpu_sample(max_rows=1024)
         if i >= args.warmup:
             vals.append(v)
+            times.append((time.perf_counter() - t0) * 1e3)
     v = float(np.mean(vals))
     line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(times)), "higher_is_better": True,
             "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl.desc},
+            "config": {"workload": wl.desc, "parallelism": "host CPU threads",
+                       "step": "one bounded sample of the workload: " + sample},
             "cpu_baseline": {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
                              "sample": sample + "; the reference project has no implementation of this path"},
             "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
