@@ -16,8 +16,18 @@
 // aliases the first 64 columns of S_t.  tcgen05.mma executes in issue order, so the
 // commit that publishes S_t(j) also proves O_t += P_t V (j-1) has finished.
 //
+// Two instantiations.  In the plain one a CTA computes one work unit (blockIdx.x).  In the
+// persistent one the grid is one CTA per SM and every CTA pulls units from a global counter
+// (the TMA thread fetches, the other roles read the unit from a two-slot shared-memory
+// mailbox); barrier phases then run on across units, Q's buffer is handed back as soon as the
+// unit's last score product has run, and the next unit's Q, first K/V tiles and first score
+// products execute under the current unit's last softmax, PV and output store.
+//
 // Algorithmic work (causal): 4 * B * H * S^2 * D / 2 flop; traffic (Q + K + V + O) * 2 B.
 #include <math.h>
+#include <stdlib.h>
+
+#include <algorithm>
 
 #include "hb_internal.h"
 #include "hb_ptx.cuh"
@@ -44,6 +54,8 @@ struct AttnParams {
   float scale_log2;             // scale * log2(e)
   float scale;
   int n_qblocks;                // ceil(S / 256)
+  int n_units;                  // B * Hq * n_qblocks
+  int32_t* work_counter;        // persistent kernel: next unit to hand out (zero at launch)
   int32_t* status;
 };
 
@@ -52,14 +64,17 @@ struct Smem {
   static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;              // KV_STAGES tiles
   static constexpr int OFF_V = OFF_K + KV_STAGES * TILE_BYTES;
   static constexpr int OFF_BAR = OFF_V + KV_STAGES * TILE_BYTES;
-  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2][2 halves], o_full[2]
-  static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 8;
-  static constexpr int OFF_TMEM_PTR = OFF_BAR + NUM_BARS * 8;
+  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2][2 halves], o_full[2],
+  // q_empty, unit_full[2], unit_empty[2]
+  static constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 8 + 5;
+  static constexpr int OFF_UNIT = OFF_BAR + NUM_BARS * 8;           // int unit[2]: the mailbox
+  static constexpr int OFF_TMEM_PTR = OFF_UNIT + 8;
   static constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
   static constexpr int TOTAL = OFF_ABORT + 4;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
 
+template <bool PERSIST>
 __global__ void __launch_bounds__(ATTN_THREADS, 1)
 hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
@@ -78,6 +93,10 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   const uint32_t bar_s_full = bar_v_empty + KV_STAGES * 8;
   const uint32_t bar_p_ready = bar_s_full + 2 * 8;
   const uint32_t bar_o_full = bar_p_ready + 4 * 8;
+  const uint32_t bar_q_empty = bar_o_full + 2 * 8;
+  const uint32_t bar_unit_full = bar_q_empty + 8;
+  const uint32_t bar_unit_empty = bar_unit_full + 2 * 8;
+  volatile int* unit_box = reinterpret_cast<volatile int*>(smem + Smem::OFF_UNIT);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + Smem::OFF_TMEM_PTR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::OFF_ABORT);
 
@@ -86,24 +105,40 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
   // Work unit: heavy (late) query blocks of a head first; the blocks of one head run
   // together so its K/V stay in L2.
-  const int bh = blockIdx.x / p.n_qblocks;
-  const int qblk = p.n_qblocks - 1 - (blockIdx.x % p.n_qblocks);
-  const int b = bh / p.Hq;
-  const int h = bh % p.Hq;
-  const int hk = h / (p.Hq / p.Hkv);
-  const int q0 = qblk * 2 * BQ;              // first query row of tile 0
-  // Number of KV tiles each query tile visits.
-  const int n_all = (p.S + BKV - 1) / BKV;
-  int n_t[2];
-  if (p.causal) {
-    n_t[0] = min(n_all, (q0 + BQ + BKV - 1) / BKV);
-    n_t[1] = min(n_all, (q0 + 2 * BQ + BKV - 1) / BKV);
-  } else {
-    n_t[0] = n_t[1] = n_all;
-  }
-  const bool tile1_live = (q0 + BQ) < p.S;   // tile 1 may lie wholly past the sequence
-  if (!tile1_live) n_t[1] = 0;
-  const int n_max = max(n_t[0], n_t[1]);
+  struct Unit { int b, h, hk, q0, n_t[2], n_max; bool tile1_live; };
+  auto decode = [&](int unit) {
+    Unit u;
+    const int bh = unit / p.n_qblocks;
+    const int qblk = p.n_qblocks - 1 - (unit % p.n_qblocks);
+    u.b = bh / p.Hq;
+    u.h = bh % p.Hq;
+    u.hk = u.h / (p.Hq / p.Hkv);
+    u.q0 = qblk * 2 * BQ;              // first query row of tile 0
+    // Number of KV tiles each query tile visits.
+    const int n_all = (p.S + BKV - 1) / BKV;
+    if (p.causal) {
+      u.n_t[0] = min(n_all, (u.q0 + BQ + BKV - 1) / BKV);
+      u.n_t[1] = min(n_all, (u.q0 + 2 * BQ + BKV - 1) / BKV);
+    } else {
+      u.n_t[0] = u.n_t[1] = n_all;
+    }
+    u.tile1_live = (u.q0 + BQ) < p.S;  // tile 1 may lie wholly past the sequence
+    if (!u.tile1_live) u.n_t[1] = 0;
+    u.n_max = max(u.n_t[0], u.n_t[1]);
+    return u;
+  };
+  // Consumers of the mailbox: unit number `uq` of this CTA.  The MMA thread calls it alone
+  // (`whole_warp` false); a softmax warp calls it with all lanes, every lane waits and reads,
+  // and lane 0 (`arrive`) hands the slot back once all of them have.
+  auto next_unit = [&](int uq, bool whole_warp, bool arrive, bool& ok) -> int {
+    if (!PERSIST) return uq == 0 ? (int)blockIdx.x : p.n_units;
+    const int slot = uq & 1;
+    if (!mbar_wait(bar_unit_full + slot * 8, (uq >> 1) & 1, abort_flag)) { ok = false; return p.n_units; }
+    const int unit = unit_box[slot];
+    if (whole_warp) __syncwarp();
+    if (arrive) mbar_arrive(bar_unit_empty + slot * 8);
+    return unit;
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -119,6 +154,11 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       mbar_init(bar_p_ready + (t * 2) * 8, 4);        // one arrival per softmax warp of the tile
       mbar_init(bar_p_ready + (t * 2 + 1) * 8, 4);
       mbar_init(bar_o_full + t * 8, 1);
+    }
+    mbar_init(bar_q_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_unit_full + i * 8, 1);
+      mbar_init(bar_unit_empty + i * 8, 9);           // MMA thread + one lane of each softmax warp
     }
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -136,24 +176,42 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer (+ unit hand-out)
     if (elect_one()) {
       bool ok = true;
-      mbar_arrive_expect_tx(bar_q_full, (tile1_live ? 2 : 1) * TILE_BYTES);
-      for (int t = 0; t < (tile1_live ? 2 : 1); ++t)
-        for (int c = 0; c < 2; ++c)
-          tma_load_4d(sQ + t * TILE_BYTES + c * HALF_BYTES, &tmQ, bar_q_full, c * 64, h, q0 + t * BQ, b);
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j % KV_STAGES;
-        const uint32_t ph = (j / KV_STAGES) & 1;
-        if (!mbar_wait(bar_k_empty + s * 8, ph ^ 1, abort_flag)) { ok = false; break; }
-        mbar_arrive_expect_tx(bar_k_full + s * 8, TILE_BYTES);
-        for (int c = 0; c < 2; ++c)
-          tma_load_4d(sK + s * TILE_BYTES + c * HALF_BYTES, &tmK, bar_k_full + s * 8, c * 64, hk, j * BKV, b);
-        if (!mbar_wait(bar_v_empty + s * 8, ph ^ 1, abort_flag)) { ok = false; break; }
-        mbar_arrive_expect_tx(bar_v_full + s * 8, TILE_BYTES);
-        for (int c = 0; c < 2; ++c)
-          tma_load_4d(sV + s * TILE_BYTES + c * HALF_BYTES, &tmV, bar_v_full + s * 8, c * 64, hk, j * BKV, b);
+      int g = 0;                                  // KV tiles loaded so far by this CTA: ring position
+      for (int uq = 0; ok; ++uq) {
+        int unit;
+        if (PERSIST) {
+          const int slot = uq & 1;
+          if (!mbar_wait(bar_unit_empty + slot * 8, ((uq >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          unit = atomicAdd(p.work_counter, 1);
+          if (unit > p.n_units) unit = p.n_units;
+          unit_box[slot] = unit;
+          mbar_arrive(bar_unit_full + slot * 8);
+        } else {
+          unit = uq == 0 ? (int)blockIdx.x : p.n_units;
+        }
+        if (unit >= p.n_units) break;
+        const Unit u = decode(unit);
+        // Q's buffer is free once the previous unit's last score product has run.
+        if (!mbar_wait(bar_q_empty, (uq & 1) ^ 1, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(bar_q_full, (u.tile1_live ? 2 : 1) * TILE_BYTES);
+        for (int t = 0; t < (u.tile1_live ? 2 : 1); ++t)
+          for (int c = 0; c < 2; ++c)
+            tma_load_4d(sQ + t * TILE_BYTES + c * HALF_BYTES, &tmQ, bar_q_full, c * 64, u.h, u.q0 + t * BQ, u.b);
+        for (int j = 0; j < u.n_max && ok; ++j, ++g) {
+          const int s = g % KV_STAGES;
+          const uint32_t ph = (g / KV_STAGES) & 1;
+          if (!mbar_wait(bar_k_empty + s * 8, ph ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar_k_full + s * 8, TILE_BYTES);
+          for (int c = 0; c < 2; ++c)
+            tma_load_4d(sK + s * TILE_BYTES + c * HALF_BYTES, &tmK, bar_k_full + s * 8, c * 64, u.hk, j * BKV, u.b);
+          if (!mbar_wait(bar_v_empty + s * 8, ph ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar_v_full + s * 8, TILE_BYTES);
+          for (int c = 0; c < 2; ++c)
+            tma_load_4d(sV + s * TILE_BYTES + c * HALF_BYTES, &tmV, bar_v_full + s * 8, c * 64, u.hk, j * BKV, u.b);
+        }
       }
       if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_ATTN; p.status[2] = 1; }
     }
@@ -168,8 +226,8 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       const uint64_t desc_q = umma_desc_k_sw128(sQ);
       const uint64_t desc_k = umma_desc_k_sw128(sK);
       const uint64_t desc_v = umma_desc_mn_sw128(sV, HALF_BYTES, 1024);
-      auto issue_qk = [&](int t, int j) {
-        const int s = j % KV_STAGES;
+      auto issue_qk = [&](int t, int g) {          // g: ring position of the K tile
+        const int s = g % KV_STAGES;
         const uint32_t d_tmem = tmem_base + t * 128;
         const uint64_t a_desc = desc_q + static_cast<uint32_t>(t * (TILE_BYTES >> 4));
         const uint64_t b_desc = desc_k + static_cast<uint32_t>(s * (TILE_BYTES >> 4));
@@ -180,8 +238,8 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
         }
         umma_commit<1>(bar_s_full + t * 8);
       };
-      auto issue_pv = [&](int t, int j, int hf) {     // keys [64 hf, 64 hf + 64) of the tile
-        const int s = j % KV_STAGES;
+      auto issue_pv = [&](int t, int g, int j, int hf) {     // keys [64 hf, 64 hf + 64) of KV tile j of the unit
+        const int s = g % KV_STAGES;
         const uint32_t d_tmem = tmem_base + 256 + t * 128;
         const uint32_t a_tmem = tmem_base + t * 128;     // P aliases S: 64 packed columns
         const uint64_t b_desc = desc_v + static_cast<uint32_t>(s * (TILE_BYTES >> 4));
@@ -190,39 +248,47 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
           umma_ts(d_tmem, a_tmem + kk * 8, b_desc + static_cast<uint32_t>(kk * (2048 >> 4)), idesc_pv,
                   (j | kk) != 0 ? 1u : 0u);
       };
-      if (!mbar_wait(bar_q_full, 0, abort_flag)) ok = false;
-      // Prologue: S_t(0) for both tiles.
-      if (ok && n_max > 0) {
-        if (!mbar_wait(bar_k_full, 0, abort_flag)) ok = false;
-        if (ok) {
-          tc_fence_after();
-          issue_qk(0, 0);
-          if (n_t[1] > 0) issue_qk(1, 0);
-          umma_commit<1>(bar_k_empty);   // K(0) is free once both S(0) products have read it
-        }
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j % KV_STAGES;
-        const uint32_t ph = (j / KV_STAGES) & 1;
-        const int sn = (j + 1) % KV_STAGES;
-        const uint32_t phn = ((j + 1) / KV_STAGES) & 1;
-        if (!mbar_wait(bar_v_full + s * 8, ph, abort_flag)) { ok = false; break; }
-        if (j + 1 < n_max && !mbar_wait(bar_k_full + sn * 8, phn, abort_flag)) { ok = false; break; }
-        for (int t = 0; t < 2; ++t) {
-          if (j < n_t[t]) {
-            if (!mbar_wait_spin(bar_p_ready + (t * 2) * 8, j & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(t, j, 0);
-            if (!mbar_wait_spin(bar_p_ready + (t * 2 + 1) * 8, j & 1, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(t, j, 1);
-            if (j + 1 == n_t[t]) umma_commit<1>(bar_o_full + t * 8);
+      int g0 = 0;                                  // ring position of the unit's first KV tile
+      uint32_t np[2] = {0, 0};                     // P publications consumed per tile: barrier phase
+      for (int uq = 0; ok; ++uq) {
+        const int unit = next_unit(uq, false, true, ok);
+        if (!ok || unit >= p.n_units) break;
+        const Unit u = decode(unit);
+        if (!mbar_wait(bar_q_full, uq & 1, abort_flag)) { ok = false; break; }
+        // Prologue: S_t(0) for both tiles.
+        if (!mbar_wait(bar_k_full + (g0 % KV_STAGES) * 8, (g0 / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        issue_qk(0, g0);
+        if (u.n_t[1] > 0) issue_qk(1, g0);
+        umma_commit<1>(bar_k_empty + (g0 % KV_STAGES) * 8);   // K(0) is free once both S(0) products have read it
+        if (u.n_max <= 1) umma_commit<1>(bar_q_empty);
+        for (int j = 0; j < u.n_max && ok; ++j) {
+          const int g = g0 + j;
+          const int s = g % KV_STAGES;
+          const uint32_t ph = (g / KV_STAGES) & 1;
+          const int sn = (g + 1) % KV_STAGES;
+          const uint32_t phn = ((g + 1) / KV_STAGES) & 1;
+          if (!mbar_wait(bar_v_full + s * 8, ph, abort_flag)) { ok = false; break; }
+          if (j + 1 < u.n_max && !mbar_wait(bar_k_full + sn * 8, phn, abort_flag)) { ok = false; break; }
+          for (int t = 0; t < 2; ++t) {
+            if (j < u.n_t[t]) {
+              if (!mbar_wait_spin(bar_p_ready + (t * 2) * 8, np[t] & 1, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              issue_pv(t, g, j, 0);
+              if (!mbar_wait_spin(bar_p_ready + (t * 2 + 1) * 8, np[t] & 1, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+              issue_pv(t, g, j, 1);
+              ++np[t];
+              if (j + 1 == u.n_t[t]) umma_commit<1>(bar_o_full + t * 8);
+            }
+            if (j + 1 < u.n_t[t]) issue_qk(t, g + 1);
           }
-          if (j + 1 < n_t[t]) issue_qk(t, j + 1);
+          if (!ok) break;
+          umma_commit<1>(bar_v_empty + s * 8);
+          if (j + 1 < u.n_max) umma_commit<1>(bar_k_empty + sn * 8);
+          if (j + 2 == u.n_max) umma_commit<1>(bar_q_empty);   // every score product of the unit has been issued
         }
-        if (!ok) break;
-        umma_commit<1>(bar_v_empty + s * 8);
-        if (j + 1 < n_max) umma_commit<1>(bar_k_empty + sn * 8);
+        g0 += u.n_max;
       }
       if (!ok && p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_ATTN; p.status[2] = 2; }
     }
@@ -231,16 +297,23 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const int t = warp >> 2;                    // query tile of this warpgroup
     const int qd = warp & 3;                    // TMEM lane quarter
     const int r = qd * 32 + lane;               // row within the tile
-    const int row = q0 + t * BQ + r;            // global query row
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const uint32_t tS = tmem_base + lane_off + t * 128;
     const uint32_t tO = tmem_base + lane_off + 256 + t * 128;
+    bool ok = true;
+    uint32_t ns = 0;                            // S tiles consumed by this warp: barrier phase
+    uint32_t no = 0;                            // units whose O this warp has stored
+    for (int uq = 0; ok; ++uq) {
+    const int unit = next_unit(uq, true, lane == 0, ok);
+    if (!ok || unit >= p.n_units) break;
+    const Unit u = decode(unit);
+    const int row = u.q0 + t * BQ + r;          // global query row
+    const int b = u.b, h = u.h;
     float m_ref = -INFINITY;                    // reference max (raw score units)
     float l = 0.f;                              // running sum of exp2
-    bool ok = true;
-    const int n_mine = n_t[t];
-    for (int j = 0; j < n_mine && ok; ++j) {
-      if (!mbar_wait(bar_s_full + t * 8, j & 1, abort_flag)) { ok = false; break; }
+    const int n_mine = u.n_t[t];
+    for (int j = 0; j < n_mine && ok; ++j, ++ns) {
+      if (!mbar_wait(bar_s_full + t * 8, ns & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       uint32_t sv[128];
 #pragma unroll
@@ -316,7 +389,8 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     }
     // ---- epilogue: O / l -> bf16 -> global
     if (ok && n_mine > 0) {
-      if (!mbar_wait(bar_o_full + t * 8, 0, abort_flag)) ok = false;
+      if (!mbar_wait(bar_o_full + t * 8, no & 1, abort_flag)) ok = false;
+      ++no;
     }
     if (ok && n_mine > 0) {
       tc_fence_after();
@@ -343,6 +417,7 @@ hb_attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       if (p.lse && row < p.S)
         p.lse[(static_cast<int64_t>(b) * p.Hq + h) * p.S + row] = m_ref * p.scale + logf(l);
     }
+    }   // units
     if (!ok && p.status && lane == 0) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_ATTN; p.status[2] = 3; }
   }
 
@@ -411,17 +486,36 @@ extern "C" hb_status hb_attention(hb_ctx* ctx, const hb_tensor* Q, const hb_tens
   p.scale_log2 = opts->scale * 1.4426950408889634f;
   p.n_qblocks = (int)((S + 2 * BQ - 1) / (2 * BQ));
   p.status = ctx->d_status;
-  const int64_t grid = B * Hq * p.n_qblocks;
-  if (grid > INT32_MAX) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention: too many work units");
+  const int64_t units = B * Hq * p.n_qblocks;
+  if (units >= INT32_MAX - 4096) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention: too many work units");
+  p.n_units = (int)units;
+  // Persistent form when every SM would otherwise run several CTAs in a row; the environment
+  // variable HB_ATTN_PERSISTENT=0/1 overrides.  Each launch takes the next of a few work
+  // counters so that launches in flight on different streams never share one.
+  bool persist = units >= 2 * (int64_t)ctx->sm_count;
+  if (const char* e = getenv("HB_ATTN_PERSISTENT")) persist = atoi(e) != 0;
+  p.work_counter = nullptr;
+  if (persist) {
+    p.work_counter = ctx->d_status + 8 + (ctx->attn_launches++ & 7);
+    cudaError_t e = cudaMemsetAsync(p.work_counter, 0, sizeof(int32_t), ctx->stream);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaMemsetAsync(attention work counter)");
+  }
+  const int64_t grid = persist ? std::min<int64_t>(units, ctx->sm_count) : units;
 
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(hb_attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(hb_attention_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Smem::DYN_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(hb_attention_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               Smem::DYN_BYTES);
     if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(attention)");
     attr_set[ctx->device & 63] = true;
   }
-  hb_attention_fwd_kernel<<<(unsigned)grid, ATTN_THREADS, Smem::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
+  if (persist)
+    hb_attention_fwd_kernel<true><<<(unsigned)grid, ATTN_THREADS, Smem::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
+  else
+    hb_attention_fwd_kernel<false><<<(unsigned)grid, ATTN_THREADS, Smem::DYN_BYTES, ctx->stream>>>(tmQ, tmK, tmV, p);
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "attention launch");
 }

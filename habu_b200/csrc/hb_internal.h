@@ -49,6 +49,7 @@ struct hb_ctx {
   cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
   std::vector<cudaEvent_t> event_pool;
   int32_t* d_status = nullptr;
+  uint32_t attn_launches = 0;   // picks one of the attention work counters kept behind the status words
   int32_t* h_status = nullptr;        // pinned
   int* d_tickets = nullptr;           // split-K arrival tickets, one per output tile, zero between launches
   int64_t launches = 0;

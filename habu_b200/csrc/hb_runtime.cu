@@ -35,8 +35,8 @@ extern "C" hb_status hb_ctx_create(int32_t device, hb_ctx** out) {
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
   if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaMalloc(&ctx->d_status, 4 * sizeof(int32_t)) != cudaSuccess ||
-      cudaMemset(ctx->d_status, 0, 4 * sizeof(int32_t)) != cudaSuccess ||
+      cudaMalloc(&ctx->d_status, 16 * sizeof(int32_t)) != cudaSuccess ||     // 4 status words, 4 spare, 8 work counters
+      cudaMemset(ctx->d_status, 0, 16 * sizeof(int32_t)) != cudaSuccess ||
       cudaMalloc(&ctx->d_tickets, HB_MAX_SPLITK_TILES * sizeof(int)) != cudaSuccess ||
       cudaMemset(ctx->d_tickets, 0, HB_MAX_SPLITK_TILES * sizeof(int)) != cudaSuccess ||
       cudaMallocHost(&ctx->h_status, 4 * sizeof(int32_t)) != cudaSuccess) {

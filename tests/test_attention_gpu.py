@@ -130,6 +130,28 @@ def test_host_entry_point_pipelines_batch_groups(ctx):
         ctx.free(t)
 
 
+def test_persistent_and_one_unit_per_cta_kernels_agree_bit_for_bit(ctx, monkeypatch):
+    # the persistent kernel (CTAs pull work units from a counter) is chosen for large launches;
+    # HB_ATTN_PERSISTENT forces either form.  Same arithmetic per unit, so identical bits.
+    B, S, HQ, HKV, D = 2, 700, 4, 2, 128          # 24 units, ragged last block, grouped-query heads
+    Q, Qb = bf16_normal((B, S, HQ, D), SEED + 71)
+    K, Kb = bf16_normal((B, S, HKV, D), SEED + 72)
+    V, Vb = bf16_normal((B, S, HKV, D), SEED + 73)
+    dQ, dK, dV = ctx.upload(Qb), ctx.upload(Kb), ctx.upload(Vb)
+    outs = []
+    for mode in ("0", "1", "1"):
+        monkeypatch.setenv("HB_ATTN_PERSISTENT", mode)
+        dO = ctx.attention(dQ, dK, dV)
+        ctx.sync()
+        outs.append(ctx.download(dO))
+        ctx.free(dO)
+    monkeypatch.delenv("HB_ATTN_PERSISTENT")
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+    assert max_abs(oracle.from_bf16_bits(outs[1]), oracle.attention(Q, K, V)) < TOL
+    for t in (dQ, dK, dV):
+        ctx.free(t)
+
+
 def test_invalid_arguments(ctx):
     q = ctx.empty((1, 128, 3, 128))
     k = ctx.empty((1, 128, 2, 128))
