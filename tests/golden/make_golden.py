@@ -22,7 +22,7 @@ from util import SEED, bf16_normal  # noqa: E402
 
 
 def cases():
-    """name -> (inputs dict, expected output).  Shared with tests/test_golden.py."""
+    """name -> (inputs dict, expected output).  Shared with tests/test_y_golden.py."""
     out = {}
     # bf16 GEMM 128 x 256 x 64, B column-major (given as [N, K])
     A, _ = bf16_normal((128, 64), SEED + 1, 64 ** -0.5)
