@@ -101,6 +101,7 @@ def load() -> C.CDLL:
         "hb_p2p_attach": [vp, i32, i32, vp, C.c_size_t],
         "hb_p2p_attach_external": [vp, i32, i32, C.POINTER(vp), vp, C.c_size_t],
         "hb_all_reduce": [vp, vp, i64, i32, i32],
+        "hb_comm_set_wait_limit": [vp, C.c_uint32],
         "hb_all_reduce_async": [vp, vp, i64, i32, i32],
         "hb_side_join": [vp],
         "hb_all_reduce_norm": [vp, vp, vp, vp, vp, vp, i64, i64, f32, i32, i32],

@@ -67,7 +67,6 @@ constexpr int AR_MAX_WORLD = 8;
 constexpr int AR_MAX_CTAS = 296;                       // 2 per SM on a 148-SM part
 constexpr int AR_THREADS = 256;
 constexpr size_t AR_FLAG_BYTES = 2 * AR_MAX_CTAS * AR_MAX_WORLD * sizeof(uint32_t);
-constexpr uint32_t AR_SPIN_LIMIT = 1u << 24;
 
 struct ArParams {
   void* peers[AR_MAX_WORLD];      // base of every rank's symmetric buffer (data first)
@@ -76,6 +75,7 @@ struct ArParams {
   int64_t count;                  // elements
   int world, rank;
   uint32_t epoch;
+  uint32_t spin_limit;            // polls per flag wait before the kernel gives up
   int32_t* status;
 };
 
@@ -106,7 +106,7 @@ __device__ bool ar_barrier(const ArParams& p, int phase, int cta) {
     uint32_t it = 0;
     // epochs only grow; a peer that is already one call ahead has also passed this one
     while (static_cast<int32_t>(ld_acquire_sys(mine) - p.epoch) < 0) {
-      if (++it > AR_SPIN_LIMIT) { failed = 1; break; }
+      if (++it > p.spin_limit) { failed = 1; break; }
     }
   }
   __syncthreads();
@@ -373,6 +373,13 @@ extern "C" hb_status hb_p2p_attach(hb_ctx* ctx, int32_t world, int32_t rank, con
 
 extern "C" size_t hb_p2p_flag_bytes(void) { return AR_FLAG_BYTES; }
 
+extern "C" hb_status hb_comm_set_wait_limit(hb_ctx* ctx, uint32_t polls) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (polls == 0) return hb_fail(ctx, HB_ERR_INVALID, "comm: the wait limit must be at least one poll");
+  ctx->p2p.spin_limit = polls;
+  return HB_OK;
+}
+
 // Registers a symmetric buffer the caller allocated and mapped: peer_ptrs[r] is rank r's
 // buffer as seen from this process (peer_ptrs[rank] the local one), `multicast_ptr` the
 // NVSwitch multicast mapping of the same buffer or NULL.  Each buffer must hold `bytes`
@@ -442,6 +449,7 @@ extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32
   p.world = s.world;
   p.rank = s.rank;
   p.epoch = ++s.epoch;
+  p.spin_limit = s.spin_limit;
   p.status = ctx->d_status;
   const int64_t nvec = count / (16 / es);
   int64_t want = (nvec / s.world + AR_THREADS - 1) / AR_THREADS;
@@ -649,6 +657,7 @@ extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const 
   p.ar.world = s.world;
   p.ar.rank = s.rank;
   p.ar.epoch = ++s.epoch;
+  p.ar.spin_limit = s.spin_limit;
   p.ar.status = ctx->d_status;
   p.out_off = static_cast<const char*>(out) - lo;
   p.mc = static_cast<char*>(s.multicast);

@@ -413,8 +413,16 @@ hb_status static_fail(hb_status code, const char* msg, const char* detail = "") 
 // In host code the array names above are host-side stand-ins, not device addresses; the
 // address a kernel can use comes from cudaGetSymbolAddress, per device, with that device
 // current.
+// cudaGetSymbolAddress (like the status copies of hb_static_status) acts on the calling
+// thread's CURRENT device, so a `device` that is not current is refused here, for every
+// entry point: otherwise another GPU's addresses would be cached under `device`.
 hb_status static_setup(int device, StaticDev** out) {
   if (device < 0 || device >= 64) return static_fail(HB_ERR_INVALID, "skinny_static: device index out of range");
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess || cur != device) {
+    cudaGetLastError();
+    return static_fail(HB_ERR_INVALID, "skinny_static: `device` must be the current CUDA device of the calling thread");
+  }
   std::lock_guard<std::mutex> lock(g_static_mu);
   StaticDev& d = g_static_dev[device];
   if (!d.ready) {
@@ -446,9 +454,6 @@ extern "C" hb_status hb_matmul_skinny_static(const void* A, const void* B, void*
   if (M > MAX_MPAD) return static_fail(HB_ERR_UNSUPPORTED, "skinny_static: M must be at most 64");
   if (K % 8 || N % 8) return static_fail(HB_ERR_UNSUPPORTED, "skinny_static: N and K must be multiples of 8");
   if (N > INT32_MAX || K > INT32_MAX) return static_fail(HB_ERR_UNSUPPORTED, "skinny_static: dimension exceeds 2^31-1");
-  int cur = -1;
-  if (cudaGetDevice(&cur) != cudaSuccess || cur != device)
-    return static_fail(HB_ERR_INVALID, "skinny_static: `device` must be the current CUDA device of the calling thread");
   StaticDev* d = nullptr;
   hb_status st = static_setup(device, &d);
   if (st != HB_OK) return st;

@@ -281,7 +281,7 @@ extern "C" hb_status hb_rope(hb_ctx* ctx, void* x, int64_t tokens, int64_t seq, 
     cudaError_t e = cudaSetDevice(ctx->device);
     if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaSetDevice");
     if (bytes > ctx->rope_table_bytes) {
-      if (ctx->rope_table) { cudaStreamSynchronize(ctx->stream); cudaFree(ctx->rope_table); ctx->rope_table = nullptr; }
+      if (ctx->rope_table) { hb_quiesce(ctx); cudaFree(ctx->rope_table); ctx->rope_table = nullptr; }
       e = cudaMalloc(&ctx->rope_table, bytes);
       if (e != cudaSuccess) { cudaGetLastError(); ctx->rope_table_bytes = 0; return hb_fail(ctx, HB_ERR_NOMEM, "rope: cannot allocate the angle table"); }
       ctx->rope_table_bytes = bytes;

@@ -197,6 +197,14 @@ extern "C" hb_status hb_graph_add(hb_graph* g, const hb_node* n) {
       return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: %s node optional input %d names unknown tensor %d", kNodeNames[n->kind], i, n->in[i]);
   }
   if (!valid_id(g, n->out)) return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: %s node output names unknown tensor %d", kNodeNames[n->kind], n->out);
+  // Only the collective nodes may run on the side stream.  The executor orders nodes on
+  // different streams by the byte ranges of their tensors; compute nodes also share state it
+  // cannot see (the stream-K workspace and tickets, the RoPE angle table, the attention work
+  // counters), so two of them on different streams could race on it.
+  if (n->stream != 0 && n->stream != 1) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: stream must be 0 or 1");
+  if (n->stream == 1 && n->kind != HB_NODE_ALL_REDUCE && n->kind != HB_NODE_AR_NORM)
+    return hb_fail(g->ctx, HB_ERR_UNSUPPORTED, "graph: only all_reduce and all_reduce_norm nodes may run on the side stream (%s node)",
+                   kNodeNames[n->kind]);
   g->nodes.push_back(*n);
   g->planned = false;
   return HB_OK;
@@ -347,7 +355,8 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
       if (n.stream != 0) any_side = true;
       for (int k = 0; k < 4; ++k)
         if (n.in[k] >= 0)
-          foot[i].push_back(range_of(n.in[k], (n.kind == HB_NODE_RMSNORM && k == 2) || (n.kind == HB_NODE_AR_NORM && k == 3)));
+          foot[i].push_back(range_of(n.in[k], (n.kind == HB_NODE_RMSNORM && k == 2) || (n.kind == HB_NODE_AR_NORM && k == 3) ||
+                                                  (n.kind == HB_NODE_ATTENTION && k == 3)));   // inputs the node writes
       foot[i].push_back(range_of(n.out, true));
     }
     g->wait_for.assign(nn, -1);

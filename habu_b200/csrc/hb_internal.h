@@ -35,6 +35,7 @@ struct hb_p2p_state {
   void* multicast = nullptr;          // NVSwitch multicast mapping of the same buffer (optional)
   bool external = false;              // buffer and mappings are owned by the caller
   uint32_t epoch = 0;
+  uint32_t spin_limit = 1u << 24;     // polls per cross-GPU flag wait before HB_ERR_TIMEOUT
 };
 
 struct hb_ctx {
@@ -77,6 +78,8 @@ hb_status hb_check_cuda(hb_ctx* ctx, cudaError_t e, const char* what);
     cudaError_t e__ = (call);                                     \
     if (e__ != cudaSuccess) return hb_check_cuda(ctx, e__, #call); \
   } while (0)
+// Drains every stream the context may have queued work on (before freeing its memory).
+hb_status hb_quiesce(hb_ctx* ctx);
 // Grow-only scratch buffer `slot` on the context's device.
 hb_status hb_get_scratch(hb_ctx* ctx, int slot, size_t bytes, void** out);
 // Copy streams and `n` ordering events for the pipelined host-buffer entry points.

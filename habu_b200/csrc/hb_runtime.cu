@@ -137,11 +137,22 @@ extern "C" hb_status hb_sync(hb_ctx* ctx) {
 extern "C" int64_t hb_launch_count(hb_ctx* ctx) { return ctx ? ctx->launches : -1; }
 extern "C" int32_t hb_sm_count(hb_ctx* ctx) { return ctx ? ctx->sm_count : -1; }
 
+// Waits for every stream the context may have work on (the stream in use, its own stream and
+// the side stream): called before context-owned memory is freed, because a kernel queued on
+// the OTHER stream of a two-stream graph may still be using it.
+hb_status hb_quiesce(hb_ctx* ctx) {
+  HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->own_stream && ctx->own_stream != ctx->stream) HB_CUDA(ctx, cudaStreamSynchronize(ctx->own_stream));
+  if (ctx->side_stream && ctx->side_stream != ctx->stream) HB_CUDA(ctx, cudaStreamSynchronize(ctx->side_stream));
+  return HB_OK;
+}
+
 hb_status hb_get_scratch(hb_ctx* ctx, int slot, size_t bytes, void** out) {
   if (bytes > ctx->scratch_bytes[slot]) {
     HB_CUDA(ctx, cudaSetDevice(ctx->device));
     if (ctx->scratch[slot]) {
-      HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      hb_status qs = hb_quiesce(ctx);
+      if (qs != HB_OK) return qs;
       HB_CUDA(ctx, cudaFree(ctx->scratch[slot]));
       ctx->scratch[slot] = nullptr;
       ctx->scratch_bytes[slot] = 0;

@@ -308,6 +308,10 @@ class Context:
         arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
         self._check(_lib.hb_p2p_attach_external(self._h, world, rank, arr, C.c_void_p(multicast_ptr or 0), nbytes))
 
+    def comm_set_wait_limit(self, polls: int):
+        """Polls per cross-GPU flag wait before a collective kernel reports HB_ERR_TIMEOUT."""
+        self._check(_lib.hb_comm_set_wait_limit(self._h, polls))
+
     def all_reduce(self, x: Tensor, algo: int = HB_AR_AUTO) -> Tensor:
         n = 1
         for s in x.shape:

@@ -197,6 +197,13 @@ size_t hb_p2p_flag_bytes(void);
 hb_status hb_p2p_attach_external(hb_ctx* ctx, int32_t world, int32_t rank,
                                  const void* const* peer_ptrs, void* multicast_ptr, size_t bytes);
 hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, int32_t algo);
+/* Every cross-GPU flag wait inside the collective kernels polls at most `polls` times
+ * (default 2^24, a few seconds) before the kernel records HB_ERR_TIMEOUT, skips its work and
+ * returns; hb_sync then reports the time-out and the context stays usable.  A host that has
+ * its own failure detector sets a smaller limit; all ranks should use the same one.
+ * No reference counterpart (the reference reports failures as `Result` values,
+ * `src/lib/error.ml:18-26`, and never waits on a device). */
+hb_status hb_comm_set_wait_limit(hb_ctx* ctx, uint32_t polls);
 /* Overlap: hb_all_reduce_async enqueues the same allreduce on the context's high-priority
  * side stream, ordered after everything already queued on the main stream, and returns;
  * hb_side_join makes the main stream wait for the side stream.  Kernels queued between the
@@ -244,7 +251,10 @@ typedef struct hb_node {
   int32_t iparam[4];
   float fparam[2];
   int32_t stream;          /* 0: the context's stream; 1: its side stream (runs concurrently;
-                              the executor orders conflicting nodes with events) */
+                              the executor orders conflicting nodes with events).  Only
+                              HB_NODE_ALL_REDUCE and HB_NODE_AR_NORM nodes may use stream 1:
+                              compute nodes share per-context scratch that the byte-range
+                              analysis does not see */
 } hb_node;
 hb_status hb_graph_create(hb_ctx* ctx, hb_graph** out);
 hb_status hb_graph_destroy(hb_graph* g);

@@ -31,15 +31,18 @@ def make_input(cfg, seed: int = SEED):
     return oracle.round_bf16(oracle.normal((cfg.tokens, cfg.d_model), seed + 7))
 
 
-def forward(cfg, x0, layers, round_bf16=True, heads=None, ffn=None, reduce=None):
+def forward(cfg, x0, layers, round_bf16=True, heads=None, ffn=None, reduce=None, residual_fp32=False):
     """Decoder forward.  `heads=(q0,q1,k0,k1)` and `ffn=(f0,f1)` restrict the computation
     to one rank's shard, in which case `reduce` (a function summing partials across
-    ranks) must be given; with all three None the whole model is evaluated."""
+    ranks) must be given; with all three None the whole model is evaluated.
+    `residual_fp32` (bf16-storage mode only): the residual stream x is kept in fp32, as the
+    device keeps it; sublayer outputs are still rounded to bf16 before they are added."""
     rnd = (lambda a: oracle.round_bf16(np.ascontiguousarray(a, np.float32))) if round_bf16 else (lambda a: np.ascontiguousarray(a, np.float32))
     hd, B, S = cfg.head_dim, cfg.batch, cfg.seq
     q0, q1, k0, k1 = heads if heads else (0, cfg.n_q_heads, 0, cfg.n_kv_heads)
     f0, f1 = ffn if ffn else (0, cfg.ffn_hidden)
     reduce = reduce or (lambda a: a)
+    rnd_x = (lambda a: np.ascontiguousarray(a, np.float32)) if residual_fp32 else rnd
     x = x0.astype(np.float32)
     for lw in layers:
         h = rnd(oracle.rmsnorm(x, lw["g1"], cfg.eps))
@@ -52,11 +55,11 @@ def forward(cfg, x0, layers, round_bf16=True, heads=None, ffn=None, reduce=None)
                              causal=True, round_p=round_bf16)
         a = rnd(a.reshape(B * S, (q1 - q0) * hd))
         ao = reduce(rnd(oracle.gemm(a, np.ascontiguousarray(lw["wo"][:, q0 * hd:q1 * hd]).T)))
-        x = rnd(x + rnd(ao))
+        x = rnd_x(x + rnd(ao))
         h2 = rnd(oracle.rmsnorm(x, lw["g2"], cfg.eps))
         g = oracle.gemm(h2, lw["wg"][f0:f1].T)
         u = oracle.gemm(h2, lw["wu"][f0:f1].T)
         act = rnd(oracle.swiglu(np.concatenate([g, u], 1)))
         fo = reduce(rnd(oracle.gemm(act, np.ascontiguousarray(lw["wd"][:, f0:f1]).T)))
-        x = rnd(x + rnd(fo))
+        x = rnd_x(x + rnd(fo))
     return x

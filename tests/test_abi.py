@@ -56,3 +56,14 @@ def test_host_bf16_conversion_matches_the_oracle_bit_for_bit():
     x = oracle.normal((50000,), 3, 0.0, 5.0)
     x[:9] = [0.0, -0.0, np.inf, -np.inf, np.nan, 1.00390625, 1.01171875, 3.0e38, 1e-40]
     assert np.array_equal(f32_to_bf16_bits(x), oracle.to_bf16_bits(x))
+
+
+def test_static_entry_points_refuse_a_device_that_is_not_current():
+    """No GPU needed: with no current device (or another one) the look-up of the static
+    arrays must be refused, never cached under the wrong index."""
+    from habu_b200 import _capi
+    lib = _capi.load()
+    words = (ctypes.c_int32 * 4)()
+    assert lib.hb_static_status(63, words) == 1
+    assert b"current CUDA device" in lib.hb_static_last_error()
+    assert lib.hb_static_status(-1, words) == 1

@@ -7,7 +7,10 @@ them the library keeps the split-K scratch in a static device array.  This test 
 that entry point through the C ABI twice in a row and checks both results against the
 ordinary matmul node (same kernel, context-owned scratch): within the bf16 tolerance of
 the other matmul tests, and -- because the slice-ordered reduction is deterministic --
-bit for bit.  It also checks that an over-size problem is refused with a message.
+bit for bit.  The second call must also leave the amount of free device memory exactly as
+it found it (the property the entry point exists for: nothing is allocated, nothing
+freed).  It also checks that an over-size problem is refused with a message, and that a
+device index that is not the calling thread's current device is refused.
 
 Collected last on purpose, so a run that stops at the first failure has already run
 every other test.
@@ -22,6 +25,12 @@ from util import SEED, bf16_normal, max_abs
 
 pytestmark = pytest.mark.gpu
 TOL_BF16 = 2e-2
+
+
+def _free_device_bytes():
+    import torch
+    free, _ = torch.cuda.mem_get_info(0)
+    return free
 
 
 def _static(lib, dA, dB, dC, M, N, K):
@@ -43,10 +52,14 @@ def test_static_scratch_matches_the_matmul_node_twice_in_a_row(ctx, M, N, K):
     ref = oracle.gemm(A, Bt.T)
     assert max_abs(oracle.from_bf16_bits(want), ref) < TOL_BF16
     dC = ctx.empty((M, N))
+    zeros = np.zeros((M, N), np.uint16)
     for call in range(2):
-        ctx._check(model_ir._lib.hb_upload(ctx._h, dC.ptr, np.zeros((M, N), np.uint16).ctypes.data_as(C.c_void_p), M * N * 2))
+        ctx._check(model_ir._lib.hb_upload(ctx._h, dC.ptr, zeros.ctypes.data_as(C.c_void_p), M * N * 2))
         ctx.sync()
+        before = _free_device_bytes()
         _static(lib, dA, dB, dC, M, N, K)
+        if call == 1:     # the first call on a device may load the kernel image; the second allocates nothing
+            assert _free_device_bytes() == before, "the allocation-free call changed the free device memory"
         got = ctx.download(dC)
         assert max_abs(oracle.from_bf16_bits(got), ref) < TOL_BF16, call
         assert np.array_equal(got, want), call
@@ -68,4 +81,10 @@ def test_static_scratch_refuses_problems_beyond_its_size(ctx):
     assert st == 7 and b"exceeds the static scratch" in lib.hb_static_last_error()
     st = lib.hb_matmul_skinny_static(C.c_void_p(d.ptr), C.c_void_p(d.ptr), C.c_void_p(d.ptr), 65, 1024, 1024, 0, None)
     assert st == 7 and b"at most 64" in lib.hb_static_last_error()
+    # a device that is not the calling thread's current one is refused by both entry points
+    # (the static arrays' addresses are looked up on the current device)
+    words = (C.c_int32 * 4)()
+    assert lib.hb_static_status(63, words) == 1 and b"current CUDA device" in lib.hb_static_last_error()
+    st = lib.hb_matmul_skinny_static(C.c_void_p(d.ptr), C.c_void_p(d.ptr), C.c_void_p(d.ptr), 16, 1024, 1024, 63, None)
+    assert st == 1 and b"current CUDA device" in lib.hb_static_last_error()
     ctx.free(d)
