@@ -129,3 +129,56 @@ class MlpTrainer:
             ctx.adam_step(self.w32[i], self.m[i], self.v[i], self.grads[i], self.wb[i], self.step_no, self.lr, self.b1,
                           self.b2, self.eps, 1.0 / self.world)
         return self.loss
+
+    # -- checkpoint / resume ----------------------------------------------------------
+    _MAGIC = "# habu_b200 mlp checkpoint v1"
+
+    def save(self, path: str):
+        """Writes the training state: one text header line per field, a blank line, then the
+        raw little-endian fp32 tensors in order -- for each layer the master weights, the first
+        and the second Adam moment.  The bf16 compute copies are not stored: they are the
+        masters rounded to nearest even, and :meth:`load` rebuilds them."""
+        ctx = self.ctx
+        ctx.sync()
+        with open(path, "wb") as f:
+            head = [self._MAGIC, f"width {self.width}", f"layers {self.n}", f"step {self.step_no}",
+                    f"lr {self.lr!r}", f"beta1 {self.b1!r}", f"beta2 {self.b2!r}", f"eps {self.eps!r}",
+                    "dtype f32le", "order w,m,v per layer", ""]
+            f.write(("\n".join(head) + "\n").encode())
+            for i in range(self.n):
+                for t in (self.w32[i], self.m[i], self.v[i]):
+                    f.write(np.ascontiguousarray(ctx.download(t), "<f4").tobytes())
+
+    def load(self, path: str):
+        """Restores a state written by :meth:`save` into this trainer (same width and depth);
+        the next :meth:`step` then equals, bit for bit, the step the saving trainer would have
+        taken.  Raises ValueError on a foreign, truncated or mismatching file."""
+        from .model_ir import f32_to_bf16_bits
+        ctx = self.ctx
+        with open(path, "rb") as f:
+            blob = f.read()
+        cut = blob.find(b"\n\n")
+        if cut < 0 or not blob.startswith(self._MAGIC.encode()):
+            raise ValueError(f"{path}: not a habu_b200 mlp checkpoint")
+        fields = dict(line.split(" ", 1) for line in blob[:cut].decode().splitlines()[1:])
+        if int(fields["width"]) != self.width or int(fields["layers"]) != self.n:
+            raise ValueError(f"{path}: checkpoint is {fields['layers']} x {fields['width']}, trainer is {self.n} x {self.width}")
+        body = memoryview(blob)[cut + 2:]
+        per = self.width * self.width * 4
+        if len(body) != 3 * self.n * per:
+            raise ValueError(f"{path}: truncated ({len(body)} tensor bytes, expected {3 * self.n * per})")
+        import ctypes as C
+        from .model_ir import _lib
+        k = 0
+        for i in range(self.n):
+            for t in (self.w32[i], self.m[i], self.v[i]):
+                a = np.frombuffer(body[k * per:(k + 1) * per], "<f4").astype(np.float32)
+                k += 1
+                ctx._check(_lib.hb_upload(ctx._h, C.c_void_p(t.ptr), a.ctypes.data_as(C.c_void_p), a.nbytes))
+                ctx.sync()
+                if t is self.w32[i]:
+                    wb = f32_to_bf16_bits(a)
+                    ctx._check(_lib.hb_upload(ctx._h, C.c_void_p(self.wb[i].ptr), wb.ctypes.data_as(C.c_void_p), wb.nbytes))
+                    ctx.sync()
+        self.step_no = int(fields["step"])
+        self.lr, self.b1, self.b2, self.eps = (float(fields[k]) for k in ("lr", "beta1", "beta2", "eps"))

@@ -118,14 +118,19 @@ CAMLprim value caml_hb_all_reduce(value ctx, value x, value algo) {
 }
 
 CAMLprim value caml_hb_autotune(value ctx, value m, value n, value k, value layout, value epi) {
-  CAMLparam0();
-  CAMLlocal1(pair);
+  /* CAMLparam takes at most five values; the sixth is registered with CAMLxparam */
+  CAMLparam5(ctx, m, n, k, layout);
+  CAMLxparam1(epi);
+  CAMLlocal2(pair, ms);
   hb_op_desc d = {HB_OP_MATMUL, HB_BF16, Long_val(m), Long_val(n), Long_val(k), Int_val(layout), Int_val(epi)};
   hb_tune_result r;
   hb_status st = hb_autotune(Ctx_val(ctx), &d, HB_TUNE_SEARCH, &r);
+  /* allocate the float first, into a registered local: an allocation inside the argument of
+   * Store_field could move `pair` after its field address had been computed */
+  ms = caml_copy_double(st == HB_OK ? r.ms : 0.0);
   pair = caml_alloc_tuple(2);
   Store_field(pair, 0, Val_int(st == HB_OK ? r.config_id : -st));
-  Store_field(pair, 1, caml_copy_double(st == HB_OK ? r.ms : 0.0));
+  Store_field(pair, 1, ms);
   CAMLreturn(pair);
 }
 CAMLprim value caml_hb_autotune_bytecode(value* argv, int argn) {

@@ -82,43 +82,118 @@ def test_loss_decreases_over_steps(ctx):
     assert losses[-1] < losses[0]
 
 
+def test_checkpoint_resume_reproduces_the_next_step_bit_for_bit(ctx, tmp_path):
+    """save -> load into a fresh trainer -> one more step: weights, moments and loss equal
+    those of the trainer that kept running."""
+    from habu_b200.autograd import MlpTrainer
+    tr, _ = _run_steps(ctx, n_steps=2)
+    path = str(tmp_path / "mlp.ckpt")
+    tr.save(path)
+    x, y = mlp.make_batch(BATCH, WIDTH)
+    dx, dy = ctx.upload(oracle.to_bf16_bits(x)), ctx.upload(oracle.to_bf16_bits(y))
+    tr.step(dx, dy)
+    ctx.sync()
+    other = MlpTrainer(ctx, WIDTH, BATCH, LAYERS, [np.zeros((WIDTH, WIDTH), np.float32)] * LAYERS)
+    other.load(path)
+    assert other.step_no == 2
+    other.step(dx, dy)
+    ctx.sync()
+    assert ctx.download(other.loss).tobytes() == ctx.download(tr.loss).tobytes()
+    for i in range(LAYERS):
+        for a, b in ((tr.w32[i], other.w32[i]), (tr.m[i], other.m[i]), (tr.v[i], other.v[i]), (tr.wb[i], other.wb[i])):
+            assert ctx.download(a).tobytes() == ctx.download(b).tobytes(), i
+    with open(path, "r+b") as f:          # a truncated file is refused
+        f.truncate(1000)
+    with pytest.raises(ValueError):
+        other.load(path)
+
+
+@pytest.mark.timeout(900)
+def test_full_size_step_matches_oracle():
+    """The benchmark's own configuration: 4 layers of width 8192, batch 4096, one forward +
+    backward + Adam step against the CPU oracle (about 6 TFLOP on the host cores)."""
+    import habu_b200 as hb
+    from habu_b200.autograd import MlpTrainer
+    width, batch, layers = 8192, 4096, 4
+    oracle.use_all_cores()
+    ctx = hb.Context(0)
+    try:
+        ws = mlp.make_weights(width, layers)
+        tr = MlpTrainer(ctx, width, batch, layers, ws)
+        x, y = mlp.make_batch(batch, width)
+        dx, dy = ctx.upload(oracle.to_bf16_bits(x)), ctx.upload(oracle.to_bf16_bits(y))
+        tr.step(dx, dy)
+        ctx.sync()
+        got_loss = float(ctx.download(tr.loss)[0])
+        wb = [oracle.round_bf16(w.copy()) for w in ws]
+        loss, grads = mlp.forward_backward(wb, x, y)
+        del wb
+        assert abs(got_loss - loss) / loss < 1e-3, (got_loss, loss)
+        for i in range(layers):
+            got = oracle.from_bf16_bits(ctx.download(tr.grads[i]))
+            scale = float(np.max(np.abs(grads[i])))
+            err = float(np.max(np.abs(got - grads[i]))) / scale
+            assert err < 2e-2, (i, err)          # bf16 gradients, compared on g / max|g|
+            # Adam fed the device's own gradient reproduces the device's weights to fp32 rounding
+            m, v = np.zeros_like(ws[i]), np.zeros_like(ws[i])
+            mlp.adam_update([ws[i]], [m], [v], [got], step=1)
+            assert np.allclose(ctx.download(tr.w32[i]), ws[i], rtol=0, atol=2e-6), i
+            assert np.array_equal(ctx.download(tr.wb[i]), oracle.to_bf16_bits(ctx.download(tr.w32[i]))), i
+            grads[i] = None
+    finally:
+        ctx.close()
+
+
 def _dp_rank(rank, world):
     import torch.distributed as dist
 
     import habu_b200 as hb
     from habu_b200.autograd import MlpTrainer
+    from mp_util import RankGuard
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    ctx = hb.Context(rank)
-    ids = [hb.Context.comm_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(ids, src=0)
-    ctx.comm_init_rank(world, rank, ids[0])
-    nbytes = MlpTrainer.grad_bytes(WIDTH, LAYERS)
-    ptr, handle = ctx.p2p_alloc(nbytes)
-    handles = [None] * world
-    dist.all_gather_object(handles, handle)
-    ctx.p2p_attach(world, rank, handles, nbytes)
-    dist.barrier()
-    tr, losses = _run_steps(ctx, world, rank, n_steps=1, trainer_kwargs={"grads_base_ptr": ptr})
-    # the summed gradient / world equals the oracle's gradient over the concatenated batch
-    ws = [oracle.round_bf16(w.copy()) for w in mlp.make_weights(WIDTH, LAYERS)]
-    xs, ys = zip(*[mlp.make_batch(BATCH, WIDTH, r) for r in range(world)])
-    _, grads_all = mlp.forward_backward(ws, np.concatenate(xs), np.concatenate(ys))
-    for i in range(LAYERS):
-        got = oracle.from_bf16_bits(ctx.download(tr.grads[i])) / world
-        assert np.max(np.abs(got - grads_all[i])) / np.max(np.abs(grads_all[i])) < 2e-2, i
-    dist.barrier()
-    x, y = mlp.make_batch(BATCH, WIDTH, rank)
-    dx, dy = ctx.upload(oracle.to_bf16_bits(x)), ctx.upload(oracle.to_bf16_bits(y))
-    for _ in range(2):
-        tr.step(dx, dy)
-    ctx.sync()
-    blobs = [None] * world
-    mine = b"".join(ctx.download(w).tobytes() for w in tr.w32)
-    dist.all_gather_object(blobs, mine)
-    assert all(b == blobs[0] for b in blobs), "weights diverged across data-parallel ranks"
-    dist.barrier()
-    ctx.close()
+    guard = RankGuard()
+    ctx = None
+    with guard:
+        ctx = hb.Context(rank)
+        ctx.comm_set_wait_limit(1 << 22)
+        ids = [hb.Context.comm_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        ctx.comm_init_rank(world, rank, ids[0])
+        nbytes = MlpTrainer.grad_bytes(WIDTH, LAYERS)
+        ptr, handle = ctx.p2p_alloc(nbytes)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        ctx.p2p_attach(world, rank, handles, nbytes)
+    if guard.agree():
+        with guard:
+            tr, losses = _run_steps(ctx, world, rank, n_steps=1, trainer_kwargs={"grads_base_ptr": ptr})
+            # the summed gradient / world equals the oracle's gradient over the concatenated batch
+            ws = [oracle.round_bf16(w.copy()) for w in mlp.make_weights(WIDTH, LAYERS)]
+            xs, ys = zip(*[mlp.make_batch(BATCH, WIDTH, r) for r in range(world)])
+            _, grads_all = mlp.forward_backward(ws, np.concatenate(xs), np.concatenate(ys))
+            for i in range(LAYERS):
+                got = oracle.from_bf16_bits(ctx.download(tr.grads[i])) / world
+                assert np.max(np.abs(got - grads_all[i])) / np.max(np.abs(grads_all[i])) < 2e-2, i
+    if guard.agree():
+        with guard:
+            x, y = mlp.make_batch(BATCH, WIDTH, rank)
+            dx, dy = ctx.upload(oracle.to_bf16_bits(x)), ctx.upload(oracle.to_bf16_bits(y))
+            for _ in range(2):
+                tr.step(dx, dy)
+            ctx.sync()
+            mine = b"".join(ctx.download(w).tobytes() for w in tr.w32)
+    if guard.agree():
+        with guard:
+            blobs = [None] * world
+            dist.all_gather_object(blobs, mine)
+            assert all(b == blobs[0] for b in blobs), "weights diverged across data-parallel ranks"
+    if ctx is not None:
+        ctx.sync() if guard.error is None and not guard.peer_failed else None
+    dist.barrier()                 # nobody unmaps its buffer while a peer's kernel may still read it
+    if ctx is not None:
+        ctx.close()
     dist.destroy_process_group()
+    guard.reraise()
 
 
 def test_two_data_parallel_ranks_stay_identical():

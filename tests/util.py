@@ -16,11 +16,11 @@ def max_abs(a, b):
     return float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64))))
 
 
-def bf16_close(got, ref, atol=2e-2):
+def bf16_close(got, ref, atol=2e-2, rel=2.0 ** -8):
     """Largest excess over the bf16-path tolerance: max-abs `atol` against the fp32
-    reference, widened by one bf16 output rounding (2^-8 relative) where |ref| is large."""
+    reference, widened by one bf16 output rounding (`rel` = 2^-8 relative) where |ref| is large."""
     ref = ref.astype(np.float64)
-    return float(np.max(np.abs(got.astype(np.float64) - ref) - (atol + np.abs(ref) * 2.0 ** -8)))
+    return float(np.max(np.abs(got.astype(np.float64) - ref) - (atol + np.abs(ref) * rel)))
 
 
 def max_rel(a, ref, eps=1e-3):
