@@ -113,6 +113,7 @@ class GemmWorkload:
         return A, Bt
 
     def setup(self, ctx, rank, pinned):
+        self.rank = rank
         A, Bt = self.host_inputs(rank)
         self.hA, self.hB = pinned(A), pinned(Bt)
         self.hC = pinned(np.empty((self.M, self.N), np.uint16))
@@ -141,16 +142,30 @@ class GemmWorkload:
                                           self.hC.ctypes.data_as(C.c_void_p), self.M, self.N, self.K, 1)
         ctx._check(st)
 
-    def cpu_sample(self, max_rows=4096):
-        """Bounded CPU sample: the first `rows` rows of the same GEMM on the oracle."""
+    def cpu_sample(self):
+        """Bounded CPU sample: the first `rows` rows of the same GEMM on the oracle.  Returns
+        (fn, units, text): fn() runs the sample once, `units` is what one run is worth in the
+        metric's unit x seconds (here Tflop), so value = units / seconds."""
         import oracle
-        rows = min(self.M, max_rows)
+        rows = min(self.M, 4096)
         A = oracle.round_bf16(oracle.normal((rows, self.K), SEED + 1, 0.0, self.K ** -0.5))
         Bt = oracle.round_bf16(oracle.normal((self.N, self.K), SEED + 2, 0.0, self.K ** -0.5))
-        t0 = time.perf_counter()
-        oracle.gemm(A, Bt.T)
-        dt = time.perf_counter() - t0
-        return 2.0 * rows * self.N * self.K / dt / 1e12, f"first {rows} of {self.M} rows of C (oracle GEMM, fp32)"
+        return (lambda: oracle.gemm(A, Bt.T)), 2.0 * rows * self.N * self.K / 1e12, \
+            f"first {rows} of {self.M} rows of C (oracle GEMM, fp32)"
+
+    def parity(self, ctx):
+        """Outside the timed region: sampled rows of the device result against the oracle."""
+        import oracle
+        A, Bt = self.host_inputs(self.rank)
+        dA, dB, dC = self.sets[0]
+        ctx.matmul(dA, dB.T, out=dC)
+        ctx.sync()
+        got = oracle.from_bf16_bits(ctx.download(dC))
+        rows = np.unique(np.linspace(0, self.M - 1, 16).astype(np.int64))
+        ref = oracle.gemm(oracle.from_bf16_bits(A[rows]), oracle.from_bf16_bits(Bt).T)
+        err = float(np.abs(got[rows] - ref).max())
+        return {"checked": f"{len(rows)} sampled rows of C against the fp32 oracle", "max_abs": err, "tolerance": 2e-2,
+                "ok": bool(err < 2e-2)}
 
 
 class AttentionWorkload:
@@ -189,17 +204,28 @@ class AttentionWorkload:
         ctx._check(model_ir._lib.hb_attention_host(ctx._h, vp(self.hQ), vp(self.hK), vp(self.hV), vp(self.hO), self.B,
                                                    self.S, self.H, self.H, self.D, 1, self.D ** -0.5))
 
-    def cpu_sample(self, max_rows=None):
+    def cpu_sample(self):
         """Bounded CPU sample: full causal attention of 4 (batch, head) pairs on the oracle."""
         import oracle
-        heads = 4 if max_rows is None else 1
+        heads = 4
         shape = (1, self.S, heads, self.D)
         Q, K, V = (oracle.round_bf16(oracle.normal(shape, SEED + 10 + i)) for i in range(3))
-        t0 = time.perf_counter()
-        oracle.attention(Q, K, V, causal=True)
-        dt = time.perf_counter() - t0
-        return (4.0 * heads * self.S * self.S * self.D / 2 / dt / 1e12,
-                f"{heads} of {self.B * self.H} (batch, head) pairs at seq {self.S} (oracle attention, fp32)")
+        return (lambda: oracle.attention(Q, K, V, causal=True)), 4.0 * heads * self.S * self.S * self.D / 2 / 1e12, \
+            f"{heads} of {self.B * self.H} (batch, head) pairs at seq {self.S} (oracle attention, fp32)"
+
+    def parity(self, ctx):
+        """Outside the timed region: two (batch, head) pairs of the device result in full."""
+        import oracle
+        ctx.attention(self.dQ, self.dK, self.dV, out=self.dO, causal=True)
+        ctx.sync()
+        got = oracle.from_bf16_bits(ctx.download(self.dO))
+        worst = 0.0
+        for b, h in ((0, 0), (self.B - 1, self.H - 1)):
+            q, k, v = (np.ascontiguousarray(oracle.from_bf16_bits(x[b:b + 1, :, h:h + 1, :])) for x in (self.hQ, self.hK, self.hV))
+            ref = oracle.attention(q, k, v, causal=True)
+            worst = max(worst, float(np.abs(got[b:b + 1, :, h:h + 1, :] - ref).max()))
+        return {"checked": "2 (batch, head) pairs in full against the fp32 oracle", "max_abs": worst, "tolerance": 2e-2,
+                "ok": bool(worst < 2e-2)}
 
 
 def attach_symmetric(ctx, rank, world, dist, nbytes):
@@ -307,19 +333,55 @@ class DecoderWorkload:
     def value(self, ms, world):
         return self.tokens / (ms * 1e-3)
 
-    def cpu_sample(self, max_rows=None):
+    def cpu_sample(self):
         """Bounded CPU sample: the same block at batch 1 x seq 256 on the oracle (fp32)."""
         from dataclasses import replace
         from oracle import decoder
-        cfg = replace(self.cfg, batch=1, seq=256 if max_rows is None else 128, n_layers=1)
+        cfg = replace(self.cfg, batch=1, seq=256, n_layers=1)
         layers = [decoder.make_layer(cfg, 0)]
         x0 = decoder.make_input(cfg)
-        t0 = time.perf_counter()
-        decoder.forward(cfg, x0, layers, round_bf16=False)
-        dt = time.perf_counter() - t0
-        return cfg.tokens / dt * (1.0 / self.cfg.n_layers), (
+        return (lambda: decoder.forward(cfg, x0, layers, round_bf16=False)), cfg.tokens / self.cfg.n_layers, (
             f"1 of {self.cfg.n_layers} layers at batch 1 x seq {cfg.seq} (oracle decoder, fp32), scaled to tokens/s of "
             f"the {self.cfg.n_layers}-layer block")
+
+    def parity(self, ctx, rank=0, world=1, dist=None):
+        """Outside the timed region, at every rank count: the first sequence (2048 tokens) of the
+        device output against the oracle at the block's real sizes, in bf16-storage mode (same
+        rounding points) and in pure fp32; and byte equality of the whole output across ranks."""
+        import hashlib
+        from dataclasses import replace
+        import oracle
+        from oracle import decoder
+        self._copy(ctx, self.dg.x0.ptr, self.hX, up=True)
+        self.dg.run()
+        ctx.sync()
+        out_bits = ctx.download(self.dg.out)
+        digest = hashlib.sha256(out_bits.tobytes()).hexdigest()
+        same = True
+        if world > 1:
+            all_d = [None] * world
+            dist.all_gather_object(all_d, digest)
+            same = all(d == all_d[0] for d in all_d)
+        if rank != 0:
+            return None
+        cfg1 = replace(self.cfg, batch=1)
+        T = cfg1.tokens
+        got = oracle.from_bf16_bits(out_bits[:T])
+        layers = [decoder.make_layer(cfg1, i) for i in range(cfg1.n_layers)]
+        x0 = oracle.from_bf16_bits(np.ascontiguousarray(self.hX[:T]))
+        ref_b = decoder.forward(cfg1, x0, layers, round_bf16=True)
+        ref_f = decoder.forward(cfg1, x0, layers, round_bf16=False)
+        scale = float(np.abs(ref_f).max())
+        e_b, e_f, e_o = (float(np.abs(a - b).max()) for a, b in ((got, ref_b), (got, ref_f), (ref_b, ref_f)))
+        excess = float(np.max(np.abs(got - ref_b) - (2e-2 + np.abs(ref_b) * 2.0 ** -7)))
+        return {"checked": f"first sequence ({T} of {self.cfg.tokens} tokens) at the block's real sizes, {world} rank(s)",
+                "max_abs_vs_bf16_storage_oracle": e_b, "max_abs_vs_fp32_oracle": e_f,
+                "bf16_storage_oracle_vs_fp32_oracle": e_o, "max_abs_ref": scale,
+                "scaled_err_vs_fp32_oracle": e_f / scale, "ranks_byte_identical": bool(same),
+                "tolerance": "vs bf16-storage oracle: 2e-2 + one bf16 ulp (2^-7 |ref|); vs fp32 oracle: 2e-2 of the output "
+                             "scale max|ref| (the block's outputs reach |x| ~ 20, where a single bf16 rounding of the "
+                             "output is 0.06 and the bf16-storage oracle itself is 0.18 from fp32, so a flat 2e-2 cannot hold)",
+                "ok": bool(excess < 0 and e_f / scale < 2e-2 and same)}
 
 
 class MlpWorkload:
@@ -376,21 +438,78 @@ class MlpWorkload:
     def value(self, ms, world):
         return self.batch * world / (ms * 1e-3)
 
-    def cpu_sample(self, max_rows=None):
-        """Bounded CPU sample: one fwd+bwd+Adam step at width 1024, batch 512 on the oracle."""
+    def cpu_sample(self):
+        """Bounded CPU sample: one fwd+bwd+Adam step at width 2048, batch 1024 on the oracle."""
         from oracle import mlp
-        width, batch = (1024, 512) if max_rows is None else (512, 256)
+        width, batch = 2048, 1024
         ws = mlp.make_weights(width, self.layers)
         x, y = mlp.make_batch(batch, width)
         m = [np.zeros_like(w) for w in ws]
         v = [np.zeros_like(w) for w in ws]
-        t0 = time.perf_counter()
-        _, grads = mlp.forward_backward(ws, x, y, round_bf16=False)
-        mlp.adam_update(ws, m, v, grads, 1)
-        dt = time.perf_counter() - t0
+
+        def fn():
+            _, grads = mlp.forward_backward(ws, x, y, round_bf16=False)
+            mlp.adam_update(ws, m, v, grads, 1)
         scale = (batch * width * width) / (self.batch * self.width * self.width)   # flop ratio sample / full step
-        return self.batch * scale / dt, (f"one step at width {width}, batch {batch} (oracle, fp32), scaled by the flop "
-                                         f"ratio to samples/s of the width-{self.width} model")
+        return fn, self.batch * scale, (f"one step at width {width}, batch {batch} (oracle, fp32), scaled by the flop "
+                                        f"ratio to samples/s of the width-{self.width} model")
+
+
+class F32GemmWorkload:
+    """fp32 GEMM C = A.B at M=N=K=256, A and B ~ U[-1,1), everything fp32 (the CPU-runnable
+    reference case).  A correctness and launch-latency case: 33.6 Mflop and 768 KiB per call."""
+    bound = "hbm"
+    kernel = "hb_gemm_f32_kernel"
+
+    def __init__(self, name="gemm_f32_256", n=256):
+        self.name, self.n = name, n
+        self.flop = 2.0 * n ** 3
+        self.bytes = 3.0 * n * n * 4
+        self.metric, self.unit = "f32_gemm_tflops", "TFLOP/s"
+        self.desc = f"fp32 GEMM M=N=K={n}, A and B uniform[-1,1), row-major, fp32 throughout"
+        self.flush_note = "steps rotate over 512 copies of A, B, C (403 MB in total, larger than L2)"
+
+    def setup(self, ctx, rank, pinned):
+        import oracle
+        from habu_b200 import HB_F32
+        n = self.n
+        self.A = oracle.uniform((n, n), SEED + 21)
+        self.B = oracle.uniform((n, n), SEED + 22)
+        self.hA, self.hB, self.hC = pinned(self.A), pinned(np.ascontiguousarray(self.B.T)), pinned(np.empty((n, n), np.float32))
+        self.sets = [(ctx.upload(self.A), ctx.upload(self.B), ctx.empty((n, n), HB_F32)) for _ in range(512)]
+        self.turn = 0
+        self.h2d, self.d2h = 2 * n * n * 4, n * n * 4
+
+    def step(self, ctx):
+        dA, dB, dC = self.sets[self.turn % len(self.sets)]
+        self.turn += 1
+        ctx.matmul(dA, dB, out=dC)
+
+    def step_e2e(self, ctx):
+        import ctypes as C
+        from habu_b200 import model_ir
+        vp = lambda a: a.ctypes.data_as(C.c_void_p)
+        ctx._check(model_ir._lib.hb_matmul_host(ctx._h, vp(self.hA), vp(self.hB), vp(self.hC), self.n, self.n, self.n, 0))
+
+    def cpu_sample(self):
+        import oracle
+        A, B = self.A, self.B
+
+        def fn():
+            for _ in range(200):
+                oracle.gemm(A, B)
+        return fn, 200 * self.flop / 1e12, "200 repetitions of the same 256^3 product (oracle GEMM, fp32)"
+
+    def parity(self, ctx):
+        import oracle
+        dA, dB, dC = self.sets[0]
+        ctx.matmul(dA, dB, out=dC)
+        ctx.sync()
+        got = ctx.download(dC).astype(np.float64)
+        ref = oracle.gemm(self.A, self.B, acc_double=True).astype(np.float64)
+        rel = float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-3 * np.abs(ref).max())))
+        return {"checked": "all of C against the oracle (double accumulation)", "max_rel": rel, "tolerance": 1e-4,
+                "ok": bool(rel < 1e-4)}
 
 
 WORKLOADS = {
@@ -401,31 +520,47 @@ WORKLOADS = {
     "gemm4096": lambda: GemmWorkload("gemm4096", 4096, 4096, 4096),
     "gemm1024": lambda: GemmWorkload("gemm1024", 1024, 1024, 1024),
     "skinny": lambda: GemmWorkload("skinny", 16, 8192, 8192),
+    "gemm_f32_256": lambda: F32GemmWorkload(),
 }
+DEFAULT_EXTRAS = "attention,decoder,skinny,gemm4096,gemm1024,gemm_f32_256,mlp"
+
+
+def cpu_leg(wl, reps=1):
+    """Times the workload's bounded CPU sample on all host cores: inputs are generated once,
+    outside the clock; returns (values, seconds per run, sample text, threads, build)."""
+    import oracle
+    oracle.use_all_cores()
+    native = oracle.use_native_build()
+    fn, units, sample = wl.cpu_sample()
+    vals, secs = [], []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        dt = time.perf_counter() - t0
+        vals.append(units / dt)
+        secs.append(dt)
+    build = "-O3 -march=native" if native else "-O3 -march=x86-64-v3"
+    return vals, secs, sample, oracle.num_threads(), build
 
 
 def run_reference(args, rank, world):
-    """Reference arm: the CPU oracle (port) on all host threads, bounded sample per step."""
+    """Reference arm: the reference project has no implementation of this path, so its stand-in
+    is the CPU oracle (a port) on all host threads.  One step = one run of the same bounded
+    sample the other arm's cpu_baseline uses; inputs are generated once, and `value` and
+    `ms_per_step` come from the same clock (value x ms_per_step = the sample's work)."""
     if rank != 0:
         return
-    import oracle
-    oracle.use_all_cores()
     wl = WORKLOADS[args.workload]()
-    vals, times = [], []
-    sample = ""
-    for i in range(args.warmup + args.steps):
-        t0 = time.perf_counter()
-        v, sample = wl.cpu_sample(max_rows=1024)
-        if i >= args.warmup:
-            vals.append(v)
-            times.append((time.perf_counter() - t0) * 1e3)
-    v = float(np.mean(vals))
+    vals, secs, sample, threads, build = cpu_leg(wl, reps=args.warmup + args.steps)
+    vals, secs = vals[args.warmup:], secs[args.warmup:]
+    ms = float(np.mean(secs)) * 1e3
+    v = float(np.mean(secs) and (np.mean([x * t for x, t in zip(vals, secs)]) / np.mean(secs)))   # work / mean time
     line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(times)), "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": wl.desc, "parallelism": "host CPU threads",
-                       "step": "one bounded sample of the workload: " + sample},
-            "cpu_baseline": {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
+                       "step": "one bounded sample of the workload: " + sample, "build": build},
+            "cpu_baseline": {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
                              "sample": sample + "; the reference project has no implementation of this path"},
             "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -437,10 +572,13 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="gemm", choices=sorted(WORKLOADS))
-    ap.add_argument("--extras", default="attention,decoder",
-                    help="comma-separated workloads also measured (device-resident leg only) and reported under 'extras'")
+    ap.add_argument("--extras", default=DEFAULT_EXTRAS,
+                    help="comma-separated workloads also measured (device-resident leg and a parity check outside the "
+                         "timed region) and reported under 'extras'; 'none' for none")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="length of the back-to-back leg of the main workload (0 skips it)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -471,7 +609,7 @@ def main():
     pinned.keep = []
 
     def measure(name, steps, warmup, full):
-        """Times one workload.  full=False: device-resident leg only."""
+        """Times one workload.  full=False: device-resident leg and parity check only."""
         ctx = hb.Context(local_rank)
         ctx.set_stream(stream.cuda_stream)
         wl = WORKLOADS[name]()
@@ -502,6 +640,22 @@ def main():
                 dist.all_reduce(ms, op=dist.ReduceOp.MAX)
             return float(ms.item())
 
+        def roofline(kern_ms, sustained):
+            if sharded:
+                # per-GPU share of the algorithmic work (strong scaling splits it, weak repeats it)
+                achieved = wl.flop / (world if strong else 1) / (kern_ms * 1e-3) / 1e12
+            else:
+                achieved = wl.flop / (kern_ms * 1e-3) / 1e12
+            if wl.bound == "tensor":
+                peak = pk["bf16_sustained"] if sustained else pk["bf16_burst"]
+                return {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                        "peak_kind": ("sustained" if sustained else "burst") + " cuBLAS bf16, of " + pk["source"],
+                        "frac_of_burst_peak": achieved / pk["bf16_burst"],
+                        "frac_of_sustained_peak": achieved / pk["bf16_sustained"]}
+            achieved = wl.bytes / (kern_ms * 1e-3) / 1e9
+            return {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm"], "peak_kind": "STREAM-style copy, of " + pk["source"]}
+
         for _ in range(warmup):
             wl.step(ctx)
         sampler = ClockSampler(local_rank)
@@ -512,30 +666,11 @@ def main():
         launches = ctx.launches - l0
         clocks = sampler.stop() if rank == 0 else None
         ms_per_step = total_ms / steps
-        kern_ms = ms_per_step
-        if sharded:
-            value = wl.value(kern_ms, world)
-            # per-GPU share of the algorithmic work (strong scaling splits it, weak repeats it)
-            achieved = wl.flop / (world if strong else 1) / (kern_ms * 1e-3) / 1e12
-        else:
-            value = wl.flop * world / (kern_ms * 1e-3) / 1e12
-            achieved = wl.flop / (kern_ms * 1e-3) / 1e12
-        # Which measured peak applies: the burst figure for a short timed region, the sustained
-        # (power-capped) one for a region of a second or more.  Both fractions are reported.
-        long_run = total_ms > 1000.0
-        if wl.bound == "tensor":
-            peak = pk["bf16_sustained"] if long_run else pk["bf16_burst"]
-            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "peak_kind": ("sustained" if long_run else "burst") + " cuBLAS bf16, of " + pk["source"],
-                    "frac_of_burst_peak": achieved / pk["bf16_burst"],
-                    "frac_of_sustained_peak": achieved / pk["bf16_sustained"]}
-        else:
-            achieved = wl.bytes / (kern_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                    "frac": achieved / pk["hbm"], "peak_kind": "STREAM-style copy, of " + pk["source"]}
+        value = wl.value(ms_per_step, world) if sharded else wl.flop * world / (ms_per_step * 1e-3) / 1e12
+        roof = roofline(ms_per_step, total_ms > 1000.0)
         roof["traffic"] = NCU_TRAFFIC_BYTES.get(wl.name)
         roof["kernel"] = wl.kernel
-        roof["kernel_ms"] = kern_ms
+        roof["kernel_ms"] = ms_per_step
         if sharded:
             roof["note"] = "whole-step figure: algorithmic flop of the block / (n_gpus x step time), all kernels and collectives included"
         if hasattr(wl, "comm"):
@@ -543,6 +678,20 @@ def main():
         res = {"metric": wl.metric, "value": value, "unit": wl.unit, "ms_per_step": ms_per_step, "steps": steps,
                "scaling": getattr(wl, "scaling", "weak"), "workload": wl.desc, "l2": wl.flush_note, "roofline": roof,
                "gpu_launches": launches, "clocks": clocks}
+        if full and args.sustained_seconds > 0:
+            # the same step back to back for about two seconds: the power-capped regime, against the
+            # sustained cuBLAS figure; the clock sampler runs across it
+            n = max(steps, int(np.ceil(args.sustained_seconds * 1e3 / ms_per_step)))
+            sampler = ClockSampler(local_rank)
+            if rank == 0:
+                sampler.start()
+            sus_ms = timed(wl.step, n) / n
+            sus = roofline(sus_ms, True)
+            sus.update({"ms_per_step": sus_ms, "steps": n, "seconds": sus_ms * n / 1e3,
+                        "value": wl.value(sus_ms, world) if sharded else wl.flop * world / (sus_ms * 1e-3) / 1e12})
+            if rank == 0:
+                sus["clocks"] = sampler.stop()
+            roof["sustained"] = sus
         if full:
             e2e_steps = max(3, min(steps, 10))
             wl.step_e2e(ctx)
@@ -550,12 +699,16 @@ def main():
             e2e_value = wl.value(e2e_ms, world) if sharded else wl.flop * world / (e2e_ms * 1e-3) / 1e12
             res["e2e"] = {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
                           "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms}
-            if world == 1 and rank == 0 and not args.no_cpu_baseline:
-                import oracle
-                oracle.use_all_cores()
-                v, sample = wl.cpu_sample()
-                res["cpu_baseline"] = {"value": v, "unit": wl.unit, "cores": oracle.num_threads(), "kind": "port",
-                                       "sample": sample}
+        # correctness of what was just timed, outside the timed region
+        if hasattr(wl, "parity"):
+            barrier()
+            par = wl.parity(ctx, rank, world, dist) if sharded else (wl.parity(ctx) if rank == 0 else None)
+            if par is not None:
+                res["parity"] = par
+        if full and world == 1 and rank == 0 and not args.no_cpu_baseline:
+            vals, secs, sample, threads, build = cpu_leg(wl)
+            res["cpu_baseline"] = {"value": vals[0], "unit": wl.unit, "cores": threads, "kind": "port",
+                                   "sample": sample, "seconds": secs[0], "build": build}
         barrier()
         ctx.close()
         pinned.keep.clear()
@@ -563,10 +716,11 @@ def main():
 
     main_res = measure(args.workload, args.steps, args.warmup, True)
     extras = {}
-    for name in [e for e in args.extras.split(",") if e and e != args.workload]:
+    names = [] if args.extras == "none" else [e for e in args.extras.split(",") if e and e != args.workload]
+    for name in names:
         r = measure(name, max(3, min(args.steps, 20)), 3, False)
-        extras[name] = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "scaling", "roofline",
-                                          "gpu_launches")}
+        extras[name] = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "scaling", "workload", "l2",
+                                          "roofline", "gpu_launches", "parity") if k in r}
     if rank == 0:
         line = {"metric": main_res["metric"], "value": main_res["value"], "unit": main_res["unit"], "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_res["ms_per_step"],
@@ -579,8 +733,9 @@ def main():
                            "l2": main_res["l2"], "seed": SEED},
                 "roofline": main_res["roofline"], "e2e": main_res["e2e"], "gpu_launches": main_res["gpu_launches"],
                 "clocks": main_res["clocks"], "extras": extras}
-        if "cpu_baseline" in main_res:
-            line["cpu_baseline"] = main_res["cpu_baseline"]
+        for k in ("parity", "cpu_baseline"):
+            if k in main_res:
+                line[k] = main_res[k]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -28,18 +28,46 @@ def _load():
     return C.CDLL(_SO)
 
 
-_lib = _load()
+def _bind(lib):
+    lib.orc_mse.restype = C.c_double
+    lib.orc_num_threads.restype = C.c_int
+    return lib
+
+
+_lib = _bind(_load())
 _fp = C.POINTER(C.c_float)
 _i64 = C.c_int64
+_native = False
+
+
+def use_native_build() -> bool:
+    """For the timed CPU legs of ``bench.py`` only: rebuild the checker with ``-march=native``
+    on the host it is about to be timed on (AVX-512 where the host has it) and switch this
+    module to that build.  The portable x86-64-v3 build stays the one the tests use, so the
+    golden fixtures do not depend on the host's vector width.  Returns False, leaving the
+    portable build in place, when the host has no compiler or the build fails."""
+    global _lib, _native
+    if _native:
+        return True
+    so = os.path.join(_HERE, "libhb_oracle_native.so")
+    try:
+        subprocess.run(["make", "-C", _HERE, "-s", "-B", "libhb_oracle_native.so"], check=True,
+                       stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL, timeout=300)
+        lib = _bind(C.CDLL(so))
+        lib.orc_set_num_threads(C.c_int(num_threads()))
+    except Exception:
+        return False
+    _lib, _native = lib, True
+    return True
+
+
+def is_native_build() -> bool:
+    return _native
 
 
 def _f(a):
     assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"], (a.dtype, a.flags)
     return a.ctypes.data_as(_fp)
-
-
-_lib.orc_mse.restype = C.c_double
-_lib.orc_num_threads.restype = C.c_int
 
 
 def num_threads() -> int:
