@@ -625,6 +625,123 @@ hb_allreduce_norm_kernel(const ArnParams p) {
   ar_barrier(p.ar, 1, cta);
 }
 
+
+// Warp-per-row form of the same kernel for cols <= 4096 (the decoder's width).  A CTA-wide
+// barrier per row kept only two rows (16 KB) in flight per CTA; a switch or peer round trip is
+// several microseconds, so the kernel ran at less than half the NVLink rate.  Here every warp
+// owns whole rows: its 32 lanes hold the row (up to 16 x 16 B per lane), reduce the sum of
+// squares with shuffles only, and the eight warps of a CTA work on eight different rows at
+// different phases, so loads of some rows overlap the stores of others with no barrier between
+// them.  Few CTAs are needed (rows / 8 at most), which leaves the SMs to a GEMM that runs
+// beside it.  The arithmetic and its order are those of the CTA-per-row kernel and of
+// rmsnorm_kernel (lane l of virtual warp w sums vectors c = 32 (w + 8 k) + l, k = 0..3; then
+// the shuffle tree; then the eight warp sums in order), so the results are the same bits.
+constexpr int ARW_VEC = 16;    // 16-byte vectors per lane: cols <= 32 * 16 * 8 = 4096
+
+template <bool NVLS, int WORLD>
+__global__ void __launch_bounds__(AR_THREADS, 1)
+hb_allreduce_norm_rows_kernel(const ArnParams p) {
+  const int cta = blockIdx.x;
+  if (!ar_barrier(p.ar, 0, cta)) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per = p.rows / p.ar.world;
+  const int row0 = per * p.ar.rank;
+  const int nwarps = gridDim.x * (AR_THREADS / 32);
+  for (int row = row0 + cta * (AR_THREADS / 32) + warp; row < row0 + per; row += nwarps) {
+    const int64_t base = static_cast<int64_t>(row) * p.cols8;
+    uint4 s[ARW_VEC];
+    if (NVLS) {
+#pragma unroll
+      for (int k = 0; k < ARW_VEC; ++k) {
+        const int c = lane + 32 * k;
+        if (c < p.cols8) s[k] = multimem_ld_reduce_bf16(p.mc + p.ar.data_off + (base + c) * 16);
+      }
+    } else {
+#pragma unroll 2
+      for (int k = 0; k < ARW_VEC; ++k) {
+        const int c = lane + 32 * k;
+        if (c < p.cols8) {
+          uint4 pv[WORLD];
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r)
+            if (r < p.ar.world)
+              pv[r] = *(reinterpret_cast<const uint4*>(static_cast<const char*>(p.ar.peers[r]) + p.ar.data_off) + base + c);
+          float acc[8] = {};
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r)
+            if (r < p.ar.world) Vec<__nv_bfloat16>::add(acc, pv[r]);
+          s[k] = Vec<__nv_bfloat16>::pack(acc);
+        }
+      }
+    }
+    // residual add (rounded to bf16, which is what gets normalised) and the sums of squares,
+    // one partial sum per virtual warp w = k % 8
+    float ssw[8] = {};
+#pragma unroll
+    for (int k = 0; k < ARW_VEC; ++k) {
+      const int c = lane + 32 * k;
+      if (c < p.cols8) {
+        const uint4 r4 = p.residual_in[base + c];
+        const uint32_t sw[4] = {s[k].x, s[k].y, s[k].z, s[k].w}, rw[4] = {r4.x, r4.y, r4.z, r4.w};
+        uint32_t xw[4];
+        float ss = ssw[k & 7];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&sw[j]));
+          const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[j]));
+          __nv_bfloat162 x = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+          xw[j] = *reinterpret_cast<uint32_t*>(&x);
+          const float2 xf = __bfloat1622float2(x);
+          ss += xf.x * xf.x + xf.y * xf.y;
+        }
+        ssw[k & 7] = ss;
+        s[k] = make_uint4(xw[0], xw[1], xw[2], xw[3]);
+        p.residual_out[base + c] = s[k];
+      }
+    }
+    float inv = 1.0f;
+    if (p.mode == 0) {
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        float v = ssw[w];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        tot += v;
+      }
+      inv = rsqrtf(tot * p.inv_cols + p.eps);
+    }
+#pragma unroll
+    for (int k = 0; k < ARW_VEC; ++k) {
+      const int c = lane + 32 * k;
+      if (c < p.cols8) {
+        uint4 o4 = s[k];
+        if (p.mode == 0) {
+          const uint4 g = __ldg(p.gain + c);
+          const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, xw[4] = {s[k].x, s[k].y, s[k].z, s[k].w};
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[j]));
+            const float2 xf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[j]));
+            __nv_bfloat162 h = __floats2bfloat162_rn(xf.x * inv * gf.x, xf.y * inv * gf.y);
+            o[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          o4 = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        if (NVLS) {
+          multimem_st(p.mc + p.out_off + (base + c) * 16, o4);
+        } else {
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r)
+            if (r < p.ar.world) *(reinterpret_cast<uint4*>(static_cast<char*>(p.ar.peers[r]) + p.out_off) + base + c) = o4;
+        }
+      }
+    }
+  }
+  ar_barrier(p.ar, 1, cta);
+}
+
 }  // namespace
 
 extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const void* gain, const void* residual_in,
@@ -669,6 +786,24 @@ extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const 
   p.inv_cols = 1.0f / (float)cols;
   p.eps = eps;
   p.mode = mode;
+  bool by_rows = cols <= 32 * ARW_VEC * 8;            // warp-per-row form
+  if (const char* e = getenv("HB_ARN_ROWS")) by_rows = by_rows && atoi(e) != 0;
+  if (by_rows) {
+    const int per = (int)(rows / s.world);
+    int grid = (per + AR_THREADS / 32 - 1) / (AR_THREADS / 32);
+    int cap = ctx->sm_count < AR_MAX_CTAS ? ctx->sm_count : AR_MAX_CTAS;
+    if (const char* e = getenv("HB_AR_MAX_CTAS")) {   // every rank must use the same value
+      const int v = atoi(e);
+      if (v >= 1 && v < cap) cap = v;
+    }
+    if (grid > cap) grid = cap;
+    if (algo == HB_AR_NVLS) hb_allreduce_norm_rows_kernel<true, 1><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+    else if (s.world == 2) hb_allreduce_norm_rows_kernel<false, 2><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+    else if (s.world <= 4) hb_allreduce_norm_rows_kernel<false, 4><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+    else hb_allreduce_norm_rows_kernel<false, 8><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
+    ctx->launches++;
+    return hb_check_cuda(ctx, cudaGetLastError(), "all_reduce_norm launch");
+  }
   int grid = (int)(rows / s.world);
   int cap = ctx->sm_count * 2 < AR_MAX_CTAS ? ctx->sm_count * 2 : AR_MAX_CTAS;
   if (grid > cap) grid = cap;

@@ -76,10 +76,11 @@ class Graph:
         return self._add(NODE_ALL_REDUCE, [], x, [algo], stream=stream)
 
     def all_reduce_norm(self, partial, gain, residual_in, residual_out, out, eps=1e-5, gather_only=False,
-                        algo=_capi.HB_AR_AUTO):
+                        algo=_capi.HB_AR_AUTO, stream=0):
         """Fused reduce-scatter + residual add + RMSNorm + all-gather (gather_only: publish the
-        updated residual rows instead of their norm)."""
-        return self._add(NODE_AR_NORM, [partial, gain, residual_in, residual_out], out, [int(gather_only), algo], [eps])
+        updated residual rows instead of their norm).  stream=1: on the side stream."""
+        return self._add(NODE_AR_NORM, [partial, gain, residual_in, residual_out], out, [int(gather_only), algo], [eps],
+                         stream=stream)
 
     def rmsnorm(self, x, gain, out, residual=None, eps=1e-5):
         return self._add(NODE_RMSNORM, [x, gain, residual], out, [], [eps])

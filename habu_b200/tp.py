@@ -98,8 +98,8 @@ class DecoderGraph:
         from .graph import Graph
         check_shardable(cfg, world)
         self._out_id = None
-        if fused and world > 1 and chunks == 1:
-            self._build_fused(ctx, cfg, world, rank, layers, algo)
+        if fused and world > 1:
+            self._build_fused(ctx, cfg, world, rank, layers, algo, chunks)
             return
         if cfg.batch % chunks:
             raise ValueError(f"batch {cfg.batch} does not split into {chunks} chunks")
@@ -163,49 +163,66 @@ class DecoderGraph:
             g.add(rows(x, c), pending[c], rows(out, c))
         self.symmetric_needed = None
 
-    def _build_fused(self, ctx, cfg, world, rank, layers, algo):
+    def _build_fused(self, ctx, cfg, world, rank, layers, algo, chunks=1):
         """Sequence-parallel form: each allreduce + residual add + RMSNorm becomes one fused
         node (reduce-scatter, add and norm on this rank's rows, all-gather of the normalised
-        rows); the residual stream is sharded by rows and gathered once at the end."""
+        rows); the residual stream is sharded by rows and gathered once at the end.
+
+        With ``chunks > 1`` the token rows are cut into that many row blocks and every
+        row-parallel product, its fused collective and the column-parallel product that
+        consumes the gathered rows run block by block: the collective of block c goes to the
+        executor's side stream and crosses NVLink while the tensor cores work on block c+1
+        (and, later, on the consumer of block c).  A rank owns rows/world rows of EVERY block,
+        so the sharding of the residual stream is the same in all collectives.  The values do
+        not depend on ``chunks``: every output row is computed by the same arithmetic."""
         from .graph import Graph
-        if cfg.tokens % world:
-            raise ValueError("tokens must split evenly over the ranks")
-        self.ctx, self.cfg, self.world, self.rank, self.chunks = ctx, cfg, world, rank, 1
+        if cfg.tokens % (world * chunks):
+            raise ValueError("tokens must split evenly over the ranks and row blocks")
+        self.ctx, self.cfg, self.world, self.rank, self.chunks = ctx, cfg, world, rank, chunks
         T, d, hd = cfg.tokens, cfg.d_model, cfg.head_dim
         ql, kl, fl = cfg.n_q_heads // world, cfg.n_kv_heads // world, cfg.ffn_hidden // world
         W = (ql + 2 * kl) * hd
+        Tc = T // chunks
+        side = 1 if chunks > 1 else 0
         g = self.graph = Graph(ctx)
         self.x0 = ctx.empty((T, d))
         x0 = g.input(self.x0)
         self.weights = [{k: ctx.upload(v) for k, v in lw.items()} for lw in layers]
         ws = [{k: g.input(v if k in ("g1", "g2") else v.T) for k, v in dev.items()} for dev in self.weights]
-        x = g.temp((T, d))                          # residual stream: only this rank's rows are live
+        rows = lambda t, c, n: g.view(t, c * Tc * n, (Tc, n), (n, 1)) if chunks > 1 else t   # row block c of a [T, n] tensor
+        x = g.temp((T, d))                          # residual stream: only this rank's rows of each block are live
         h = g.temp((T, d))
         g.rmsnorm(x0, ws[0]["g1"], h, eps=cfg.eps)
+        # The four exchange buffers are allocated once and reused by every layer: the planner
+        # packs by position in the node list, and a buffer that it placed over another one still
+        # being read on the side stream would make the executor serialise the two streams.
+        ao, h2, fo, nxt = (g.temp((T, d), symmetric=True) for _ in range(4))
         for li, w in enumerate(ws):
             qkv = g.temp((T, W))
-            g.matmul(h, w["wqkv"], qkv)
+            for c in range(chunks):                 # block c starts as soon as its gathered rows have landed
+                g.matmul(rows(h, c, d), w["wqkv"], rows(qkv, c, W))
             g.rope(g.view(qkv, 0, (T, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
             g.rope(g.view(qkv, ql * hd, (T, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
             v4 = lambda off, H: g.view(qkv, off, (cfg.batch, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
             attn = g.temp((T, ql * hd))
             g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
                         g.view(attn, 0, (cfg.batch, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)), causal=True)
-            ao = g.temp((T, d), symmetric=True)
-            g.matmul(attn, w["wo"], ao)
-            h2 = g.temp((T, d), symmetric=True)
-            g.all_reduce_norm(ao, w["g2"], x0 if li == 0 else x, x, h2, eps=cfg.eps, algo=algo)
+            xin = x0 if li == 0 else x
+            for c in range(chunks):
+                g.matmul(rows(attn, c, ql * hd), w["wo"], rows(ao, c, d))
+                g.all_reduce_norm(rows(ao, c, d), w["g2"], rows(xin, c, d), rows(x, c, d), rows(h2, c, d), eps=cfg.eps,
+                                  algo=algo, stream=side)
             act = g.temp((T, fl))
-            g.matmul(h2, w["wgu"], act, epilogue=_capi.HB_EPI_SWIGLU)
-            fo = g.temp((T, d), symmetric=True)
-            g.matmul(act, w["wd"], fo)
-            nxt = g.temp((T, d), symmetric=True)
-            if li + 1 < len(ws):
-                g.all_reduce_norm(fo, ws[li + 1]["g1"], x, x, nxt, eps=cfg.eps, algo=algo)
-                h = nxt
-            else:
-                g.all_reduce_norm(fo, None, x, x, nxt, gather_only=True, algo=algo)
+            last = li + 1 == len(ws)
+            for c in range(chunks):
+                g.matmul(rows(h2, c, d), w["wgu"], rows(act, c, fl), epilogue=_capi.HB_EPI_SWIGLU)
+                g.matmul(rows(act, c, fl), w["wd"], rows(fo, c, d))
+                g.all_reduce_norm(rows(fo, c, d), None if last else ws[li + 1]["g1"], rows(x, c, d), rows(x, c, d),
+                                  rows(nxt, c, d), eps=cfg.eps, gather_only=last, algo=algo, stream=side)
+            if last:
                 self._out_id = nxt
+            else:
+                h = nxt
         self.symmetric_needed = None
 
     @property
