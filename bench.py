@@ -478,6 +478,106 @@ class MlpWorkload:
                                         f"ratio to samples/s of the width-{self.width} model")
 
 
+class DecodeWorkload:
+    """Generation step of the same decoder block: 16 sequences, one new token each, against
+    key/value caches holding 2048 positions per layer (synthetic N(0,1) keys and values).  Every
+    step reads all weights and all cached keys and values once: HBM-bound.  The position stays
+    fixed from step to step (the advance node is left out), so every timed step does the same
+    work; the step is captured once and replayed."""
+    bound = "hbm"
+    kernel = "hb_gemm_skinny_kernel"       # the projections dominate: 872 MB of weights against 268 MB of cache
+    flush = None
+
+    def __init__(self, name="decode", batch=16, context=2048):
+        from habu_b200.tp import DecoderConfig
+        self.name, self.cfg, self.batch, self.context = name, DecoderConfig(), batch, context
+        self.metric, self.unit = "decode_tokens_per_s", "tokens/s"
+        self.desc = (f"decoder block x2 layers, generation step: {batch} sequences x 1 new token at context {context}, "
+                     "d_model 4096, 32 q / 8 kv heads, head_dim 128, SwiGLU 14336, bf16 weights and KV cache")
+        self.flush_note = "weights + KV cache per step (1.14 GB) exceed L2"
+        self.flop = 0.0
+
+    def setup(self, ctx, rank, pinned):
+        import oracle
+        from habu_b200.tp import DecodeGraph, decode_layer
+        from oracle import decoder
+        cfg = self.cfg
+        layers = []
+        for i in range(cfg.n_layers):
+            full = decoder.make_layer(cfg, i)
+            layers.append({k: oracle.to_bf16_bits(v) for k, v in decode_layer(full, cfg).items()})
+            del full
+        self.layers_seedable = True
+        self.dg = DecodeGraph(ctx, cfg, layers, self.batch, s_max=self.context, advance=False, len_hint=self.context)
+        for li, kv in enumerate(self.dg.kv):          # synthetic context: N(0,1) keys and values
+            n = 2 * self.batch * self.context * cfg.n_kv_heads * cfg.head_dim
+            half = n // 2
+            for part in range(2):
+                a = oracle.to_bf16_bits(oracle.normal((half,), SEED + 4000 + 10 * li + part))
+                DecoderWorkload._copy(ctx, kv.ptr + part * half * 2, a, up=True)
+                ctx.sync()
+        self.dg.set_pos(self.context - 1)
+        x = oracle.to_bf16_bits(oracle.round_bf16(oracle.normal((self.batch, cfg.d_model), SEED + 4100)))
+        self.hX, self.hO = pinned(x), pinned(np.empty_like(x))
+        DecoderWorkload._copy(ctx, self.dg.x.ptr, self.hX, up=True)
+        ctx.sync()
+        self.bytes = self.dg.bytes_per_step(self.context)
+        self.dg.capture()
+        self.h2d, self.d2h = x.nbytes, x.nbytes
+        self.rank = rank
+
+    def step(self, ctx):
+        self.dg.step()
+
+    def step_e2e(self, ctx):
+        DecoderWorkload._copy(ctx, self.dg.x.ptr, self.hX, up=True)
+        self.dg.step()
+        DecoderWorkload._copy(ctx, self.dg.out.ptr, self.hO, up=False)
+        ctx.sync()
+
+    def value(self, ms, world):
+        return self.batch * world / (ms * 1e-3)
+
+    def cpu_sample(self):
+        """Bounded CPU sample: the same step at context 256 on the oracle (fp32)."""
+        import oracle
+        from oracle import decoder
+        cfg = self.cfg
+        layers = [decoder.make_layer(cfg, i) for i in range(cfg.n_layers)]
+        L = 256
+        cache = decoder.new_cache(cfg, self.batch, L)
+        for K, V in cache:
+            K[:] = oracle.normal(K.shape, SEED + 1)
+            V[:] = oracle.normal(V.shape, SEED + 2)
+        x = oracle.round_bf16(oracle.normal((self.batch, cfg.d_model), SEED + 4100))
+        return (lambda: decoder.decode_step(cfg, x, layers, cache, L - 1, round_bf16=False)), float(self.batch), \
+            f"one generation step of {self.batch} sequences at context {L} (oracle, fp32; the weights dominate the cost)"
+
+    def parity(self, ctx):
+        """Outside the timed region: the step's output against the oracle's decode_step on the
+        same weights, cache and token (bf16-storage mode)."""
+        import oracle
+        from oracle import decoder
+        cfg = self.cfg
+        layers = [decoder.make_layer(cfg, i) for i in range(cfg.n_layers)]
+        B, L = self.batch, self.context
+        cache = []
+        for kv in self.dg.kv:
+            a = oracle.from_bf16_bits(ctx.download(kv))
+            cache.append((a[:B].copy(), a[B:].copy()))
+        x = oracle.from_bf16_bits(np.ascontiguousarray(self.hX))
+        self.dg.step()
+        ctx.sync()
+        got = oracle.from_bf16_bits(ctx.download(self.dg.out))
+        want = decoder.decode_step(cfg, x, layers, cache, L - 1, round_bf16=True)
+        scale = float(np.abs(want).max())
+        err = float(np.abs(got - want).max())
+        return {"checked": f"all {B} output rows against the oracle's decode_step (bf16-storage mode) at context {L}",
+                "max_abs": err, "max_abs_ref": scale, "scaled_err": err / scale,
+                "tolerance": "max-abs / max|ref| < 2e-2 (outputs reach |x| ~ 20: see the decoder workload)",
+                "ok": bool(err / scale < 2e-2)}
+
+
 class F32GemmWorkload:
     """fp32 GEMM C = A.B at M=N=K=256, A and B ~ U[-1,1), everything fp32 (the CPU-runnable
     reference case).  A correctness and launch-latency case: 33.6 Mflop and 768 KiB per call."""
@@ -544,8 +644,9 @@ WORKLOADS = {
     "gemm1024": lambda: GemmWorkload("gemm1024", 1024, 1024, 1024),
     "skinny": lambda: GemmWorkload("skinny", 16, 8192, 8192),
     "gemm_f32_256": lambda: F32GemmWorkload(),
+    "decode": lambda: DecodeWorkload(),
 }
-DEFAULT_EXTRAS = "attention,decoder,skinny,gemm4096,gemm1024,gemm_f32_256,mlp"
+DEFAULT_EXTRAS = "attention,decoder,skinny,gemm4096,gemm1024,gemm_f32_256,mlp,decode"
 
 
 def cpu_leg(wl, reps=1):
@@ -691,7 +792,8 @@ def main():
         launches = ctx.launches - l0
         clocks = sampler.stop() if rank == 0 else None
         ms_per_step = total_ms / steps
-        value = wl.value(ms_per_step, world) if sharded else wl.flop * world / (ms_per_step * 1e-3) / 1e12
+        own_value = sharded or not wl.flop          # workloads whose metric is not a flop rate
+        value = wl.value(ms_per_step, world) if own_value else wl.flop * world / (ms_per_step * 1e-3) / 1e12
         roof = roofline(ms_per_step, total_ms > 1000.0)
         roof["traffic"] = NCU_TRAFFIC_BYTES.get(wl.name)
         roof["kernel"] = wl.kernel
@@ -713,7 +815,7 @@ def main():
             sus_ms = timed(wl.step, n) / n
             sus = roofline(sus_ms, True)
             sus.update({"ms_per_step": sus_ms, "steps": n, "seconds": sus_ms * n / 1e3,
-                        "value": wl.value(sus_ms, world) if sharded else wl.flop * world / (sus_ms * 1e-3) / 1e12})
+                        "value": wl.value(sus_ms, world) if own_value else wl.flop * world / (sus_ms * 1e-3) / 1e12})
             if rank == 0:
                 sus["clocks"] = sampler.stop()
             roof["sustained"] = sus
@@ -721,7 +823,7 @@ def main():
             e2e_steps = max(3, min(steps, 10))
             wl.step_e2e(ctx)
             e2e_ms = timed(wl.step_e2e, e2e_steps) / e2e_steps
-            e2e_value = wl.value(e2e_ms, world) if sharded else wl.flop * world / (e2e_ms * 1e-3) / 1e12
+            e2e_value = wl.value(e2e_ms, world) if own_value else wl.flop * world / (e2e_ms * 1e-3) / 1e12
             res["e2e"] = {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
                           "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms}
         if args.node_times and hasattr(wl, "node_times"):

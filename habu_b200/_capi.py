@@ -84,6 +84,9 @@ def load() -> C.CDLL:
         "hb_static_status": [i32, C.POINTER(i32)],
         "hb_attention": [vp, T, T, T, T, C.POINTER(hb_attn_opts)],
         "hb_attention_host": [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, i32, f32],
+        "hb_rope_append": [vp, vp, i64, vp, vp, i64, i64, i64, i64, i64, f32],
+        "hb_attention_decode": [vp, vp, i64, vp, vp, vp, i64, i64, i64, i64, i64, i64, f32],
+        "hb_advance_pos": [vp, vp, i32],
         "hb_rmsnorm": [vp, vp, vp, vp, vp, i64, i64, f32],
         "hb_rope": [vp, vp, i64, i64, i64, i64, i64, f32, i64],
         "hb_embedding": [vp, vp, vp, vp, i64, i64, i64],
@@ -115,6 +118,8 @@ def load() -> C.CDLL:
         "hb_plan_arena": [i32, C.POINTER(C.c_size_t), C.POINTER(i32), C.POINTER(i32), C.POINTER(C.c_size_t),
                           C.POINTER(C.c_size_t)],
         "hb_graph_run": [vp],
+        "hb_graph_capture": [vp],
+        "hb_graph_replay": [vp],
         "hb_graph_run_timed": [vp, C.POINTER(C.c_float), i32],
         "hb_graph_describe": [vp, C.c_char_p, C.c_size_t],
         "hb_graph_tensor_ptr": [vp, i32, C.POINTER(vp)],

@@ -47,12 +47,18 @@ struct hb_graph {
   void* arena = nullptr;
   size_t arena_bytes = 0, symmetric_bytes = 0;
   bool planned = false;
+  // replay: the planned node list captured once into a CUDA graph
+  bool ran_once = false;                // scratch buffers have their final size
+  cudaGraph_t captured = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int64_t launches_per_run = 0;
 };
 
 namespace {
 
 const char* kNodeNames[] = {"matmul", "attention", "all_reduce", "rmsnorm", "rope", "embedding",
-                            "swiglu", "gelu", "add", "argmax", "all_reduce_norm"};
+                            "swiglu", "gelu", "add", "argmax", "all_reduce_norm", "rope_append", "attention_decode",
+                            "advance"};
 size_t elem_size(int dtype) { return dtype == HB_BF16 ? 2 : 4; }
 
 int root_of(const hb_graph* g, int id) {
@@ -102,6 +108,8 @@ extern "C" hb_status hb_graph_destroy(hb_graph* g) {
   cudaSetDevice(g->ctx->device);
   cudaStreamSynchronize(g->ctx->stream);
   if (g->ctx->side_stream) cudaStreamSynchronize(g->ctx->side_stream);
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->captured) cudaGraphDestroy(g->captured);
   if (g->arena) cudaFree(g->arena);
   for (cudaEvent_t e : g->events)
     if (e) cudaEventDestroy(e);
@@ -188,8 +196,8 @@ extern "C" hb_status hb_graph_view(hb_graph* g, int32_t base, int64_t offset, in
 
 extern "C" hb_status hb_graph_add(hb_graph* g, const hb_node* n) {
   if (!g || !n) return HB_ERR_INVALID;
-  if (n->kind < 0 || n->kind > HB_NODE_AR_NORM) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: unknown node kind %d", n->kind);
-  static const int n_in[] = {2, 3, 0, 2, 0, 2, 1, 1, 2, 1, 1};   // required leading inputs per kind
+  if (n->kind < 0 || n->kind > HB_NODE_ADVANCE) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: unknown node kind %d", n->kind);
+  static const int n_in[] = {2, 3, 0, 2, 0, 2, 1, 1, 2, 1, 1, 2, 3, 0};   // required leading inputs per kind
   for (int i = 0; i < 4; ++i) {
     if (i < n_in[n->kind] && !valid_id(g, n->in[i]))
       return hb_fail(g->ctx, HB_ERR_NOT_FOUND, "graph: %s node input %d names unknown tensor %d", kNodeNames[n->kind], i, n->in[i]);
@@ -356,7 +364,7 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
       for (int k = 0; k < 4; ++k)
         if (n.in[k] >= 0)
           foot[i].push_back(range_of(n.in[k], (n.kind == HB_NODE_RMSNORM && k == 2) || (n.kind == HB_NODE_AR_NORM && k == 3) ||
-                                                  (n.kind == HB_NODE_ATTENTION && k == 3)));   // inputs the node writes
+                                                  (n.kind == HB_NODE_ATTENTION && k == 3) || (n.kind == HB_NODE_ROPE_APPEND && k == 0)));   // inputs the node writes
       foot[i].push_back(range_of(n.out, true));
     }
     g->wait_for.assign(nn, -1);
@@ -393,6 +401,9 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
     }
   }
   g->planned = true;
+  g->ran_once = false;                  // addresses may have moved: a captured replay is stale
+  if (g->exec) { cudaGraphExecDestroy(g->exec); g->exec = nullptr; }
+  if (g->captured) { cudaGraphDestroy(g->captured); g->captured = nullptr; }
   if (arena_bytes) *arena_bytes = need;
   if (symmetric_bytes) *symmetric_bytes = totals[1];
   return HB_OK;
@@ -468,6 +479,36 @@ static hb_status run_node(hb_graph* g, int i) {
                                 x.shape[0], x.shape[1], n.fparam[0], n.iparam[0], n.iparam[1]);
         break;
       }
+      case HB_NODE_ROPE_APPEND: {
+        const hb_graph_tensor& x = T(n.in[0]);     // [batch, row] new-token projections
+        const hb_graph_tensor& kv = T(n.out);      // [2*batch, s_max, kv_heads, 128]
+        if (x.rank != 2 || x.stride[1] != 1 || kv.rank != 4 || !is_contiguous(kv) || kv.shape[0] != 2 * x.shape[0] ||
+            kv.shape[2] != n.iparam[1] || T(n.in[1]).dtype != HB_I32) {
+          st = hb_fail(ctx, HB_ERR_INVALID, "graph: rope_append needs qkv [batch, row], an i32 position and a contiguous cache [2*batch, s_max, kv_heads, 128]");
+          break;
+        }
+        st = hb_rope_append(ctx, x.ptr, x.stride[0], kv.ptr, static_cast<const int32_t*>(T(n.in[1]).ptr), x.shape[0], n.iparam[0],
+                            n.iparam[1], kv.shape[3], kv.shape[1], n.fparam[0]);
+        break;
+      }
+      case HB_NODE_ATTN_DECODE: {
+        const hb_graph_tensor& x = T(n.in[0]);
+        const hb_graph_tensor& kv = T(n.in[1]);
+        const hb_graph_tensor& o = T(n.out);
+        if (x.rank != 2 || x.stride[1] != 1 || kv.rank != 4 || !is_contiguous(kv) || kv.shape[0] != 2 * x.shape[0] ||
+            kv.shape[2] != n.iparam[1] || T(n.in[2]).dtype != HB_I32 || !is_contiguous(o) ||
+            numel(o) != x.shape[0] * n.iparam[0] * kv.shape[3]) {
+          st = hb_fail(ctx, HB_ERR_INVALID, "graph: attention_decode needs qkv [batch, row], a contiguous cache, an i32 position and a contiguous [batch, q_heads*128] output");
+          break;
+        }
+        st = hb_attention_decode(ctx, x.ptr, x.stride[0], kv.ptr, static_cast<const int32_t*>(T(n.in[2]).ptr), o.ptr, x.shape[0],
+                                 n.iparam[0], n.iparam[1], kv.shape[3], kv.shape[1], n.iparam[2], n.fparam[0]);
+        break;
+      }
+      case HB_NODE_ADVANCE:
+        if (T(n.out).dtype != HB_I32) { st = hb_fail(ctx, HB_ERR_INVALID, "graph: advance needs an i32 position"); break; }
+        st = hb_advance_pos(ctx, static_cast<int32_t*>(T(n.out).ptr), n.iparam[0]);
+        break;
       case HB_NODE_ARGMAX: {
         const hb_graph_tensor& x = T(n.in[0]);
         st = hb_argmax(ctx, x.ptr, static_cast<int32_t*>(T(n.out).ptr), x.shape[0], x.shape[1]);
@@ -504,7 +545,64 @@ extern "C" hb_status hb_graph_run(hb_graph* g) {
     if (two && g->needs_event[i]) cudaEventRecord(g->events[i], s);
   }
   if (two) cudaStreamWaitEvent(main_stream, g->events[g->last_side_node], 0);   // join
+  if (st == HB_OK) g->ran_once = true;
   return st;
+}
+
+// Replay.  hb_graph_capture records one run of the planned node list -- both streams, with
+// the event edges between them -- into a CUDA graph and instantiates it; hb_graph_replay then
+// enqueues the whole step with one call, which removes the per-node launch gaps that dominate
+// short steps (a decode step is about thirty kernels of a few microseconds each).
+//   - The graph must have run once eagerly since it was planned: the context's scratch buffers
+//     grow on first use, and growing (free + allocate + synchronise) is not capturable.
+//   - Everything a node reads from the host is frozen at capture time: tensor addresses,
+//     shapes, configuration choices.  Values that change from step to step must live in device
+//     memory (the decode position does).
+//   - Graphs with collective nodes are refused: the cross-GPU handshakes count calls on the
+//     host, so a replayed launch would reuse a stale count.
+//   - The RoPE angle table is rebuilt inside the captured step, so a replay does not depend on
+//     what other RoPE calls the context has served in between.
+extern "C" hb_status hb_graph_capture(hb_graph* g) {
+  if (!g) return HB_ERR_INVALID;
+  hb_ctx* ctx = g->ctx;
+  if (!g->planned) return hb_fail(ctx, HB_ERR_INVALID, "graph: call hb_graph_plan before hb_graph_capture");
+  if (!g->ran_once) return hb_fail(ctx, HB_ERR_INVALID, "graph: run the planned graph once (hb_graph_run) before capturing it");
+  for (const hb_node& n : g->nodes)
+    if (n.kind == HB_NODE_ALL_REDUCE || n.kind == HB_NODE_AR_NORM)
+      if (ctx->world > 1) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "graph: a graph with collective nodes cannot be captured");
+  if (g->exec) { cudaGraphExecDestroy(g->exec); g->exec = nullptr; }
+  if (g->captured) { cudaGraphDestroy(g->captured); g->captured = nullptr; }
+  HB_CUDA(ctx, cudaSetDevice(ctx->device));
+  HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  ctx->rope_seq = 0;                                   // the table kernel becomes part of the capture
+  const int64_t l0 = ctx->launches;
+  cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed);
+  if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaStreamBeginCapture");
+  hb_status st = hb_graph_run(g);
+  std::string inner = ctx->err;
+  cudaGraph_t graph = nullptr;
+  e = cudaStreamEndCapture(ctx->stream, &graph);
+  if (st != HB_OK) {
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    return hb_fail(ctx, st, "graph: capture failed: %s", inner.c_str());
+  }
+  if (e != cudaSuccess || !graph) { cudaGetLastError(); return hb_fail(ctx, HB_ERR_CUDA, "graph: cudaStreamEndCapture: %s", cudaGetErrorString(e)); }
+  e = cudaGraphInstantiate(&g->exec, graph, 0);
+  if (e != cudaSuccess) { cudaGraphDestroy(graph); cudaGetLastError(); return hb_fail(ctx, HB_ERR_CUDA, "graph: cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
+  g->captured = graph;
+  g->launches_per_run = ctx->launches - l0;
+  ctx->launches = l0;                                  // nothing ran: the launches were recorded, not executed
+  return HB_OK;
+}
+
+extern "C" hb_status hb_graph_replay(hb_graph* g) {
+  if (!g) return HB_ERR_INVALID;
+  if (!g->exec) return hb_fail(g->ctx, HB_ERR_INVALID, "graph: call hb_graph_capture before hb_graph_replay");
+  cudaError_t e = cudaGraphLaunch(g->exec, g->ctx->stream);
+  if (e != cudaSuccess) return hb_check_cuda(g->ctx, e, "cudaGraphLaunch");
+  g->ctx->launches += g->launches_per_run;
+  return HB_OK;
 }
 
 // Runs the graph once with a CUDA event between nodes and reports each node's device

@@ -8,22 +8,29 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/habu_b200.h"
 
 // Device status word layout (int32[4]): [0] first error code, [1] kernel tag that
 // reported it, [2] detail (e.g. which wait), [3] reserved.
-enum { HB_KTAG_GEMM = 1, HB_KTAG_ATTN = 2, HB_KTAG_ALLREDUCE = 3, HB_KTAG_SPLITK = 4 };
+enum { HB_KTAG_GEMM = 1, HB_KTAG_ATTN = 2, HB_KTAG_ALLREDUCE = 3, HB_KTAG_SPLITK = 4, HB_KTAG_DECODE = 5 };
 
 // Scratch slots: kernel workspace (split-K partials), host-call staging, autotune operands.
-enum { HB_SCRATCH_WORKSPACE = 0, HB_SCRATCH_STAGING = 1, HB_SCRATCH_TUNE = 2, HB_SCRATCH_REDUCE = 3, HB_NUM_SCRATCH = 4 };
+enum { HB_SCRATCH_WORKSPACE = 0, HB_SCRATCH_STAGING = 1, HB_SCRATCH_TUNE = 2, HB_SCRATCH_REDUCE = 3, HB_SCRATCH_DECODE = 4, HB_NUM_SCRATCH = 5 };
 
 constexpr int HB_MAX_SPLITK_TILES = 4096;
 
 struct hb_tune_entry {
   int32_t config_id;
   float ms;
+};
+
+// One encoded TMA descriptor and the arguments it was encoded from (see hb_make_tensor_map).
+struct hb_tmap_entry {
+  alignas(8) unsigned char key[128];
+  alignas(64) unsigned char map[128];
 };
 
 struct hb_p2p_state {
@@ -56,6 +63,7 @@ struct hb_ctx {
   int64_t launches = 0;
   std::string err;
   std::map<std::string, hb_tune_entry> tune_cache;
+  std::unordered_multimap<uint64_t, hb_tmap_entry> tmap_cache;   // encoded TMA descriptors by argument hash
   // collectives
   void* nccl_comm = nullptr;
   int world = 1, rank = 0;

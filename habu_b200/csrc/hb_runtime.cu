@@ -189,11 +189,25 @@ static PFN_encodeTiled get_encode_fn() {
   return fn;
 }
 
+// Encoded maps are kept per context, keyed by everything that goes into the encoding: a
+// graph replays the same few dozen (buffer, shape, box) combinations every step, and three
+// driver calls per launch are host time inside every launch gap.  The descriptor holds the
+// address, not the data, so a cached map stays valid for as long as the same address is used
+// with the same geometry.
+struct hb_tmap_key {
+  const void* base;
+  uint64_t dims[5], strides[4];
+  uint32_t box[5];
+  int32_t dt, rank, swizzle;
+  bool operator==(const hb_tmap_key& o) const { return memcmp(this, &o, sizeof(*this)) == 0; }
+};
+
 hb_status hb_make_tensor_map(hb_ctx* ctx, CUtensorMap* out, CUtensorMapDataType dt, int rank,
                              const void* base, const uint64_t* dims, const uint64_t* strides_bytes,
                              const uint32_t* box, CUtensorMapSwizzle swizzle) {
   PFN_encodeTiled fn = get_encode_fn();
   if (!fn) return hb_fail(ctx, HB_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  if (rank < 1 || rank > 5) return hb_fail(ctx, HB_ERR_INVALID, "tensor map rank %d", rank);
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0)
     return hb_fail(ctx, HB_ERR_INVALID, "tensor base address must be 16-byte aligned");
   for (int i = 0; i + 1 < rank; ++i)
@@ -201,6 +215,17 @@ hb_status hb_make_tensor_map(hb_ctx* ctx, CUtensorMap* out, CUtensorMapDataType 
       return hb_fail(ctx, HB_ERR_INVALID,
                      "tensor stride %d (%llu bytes) must be a multiple of 16 bytes", i + 1,
                      (unsigned long long)strides_bytes[i]);
+  hb_tmap_key key;
+  memset(&key, 0, sizeof(key));
+  key.base = base; key.dt = (int32_t)dt; key.rank = rank; key.swizzle = (int32_t)swizzle;
+  for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; if (i + 1 < rank) key.strides[i] = strides_bytes[i]; }
+  uint64_t h = 1469598103934665603ull;                   // FNV-1a over the key
+  for (size_t i = 0; i < sizeof(key); ++i) { h ^= reinterpret_cast<const unsigned char*>(&key)[i]; h *= 1099511628211ull; }
+  if (ctx) {
+    auto range = ctx->tmap_cache.equal_range(h);
+    for (auto it = range.first; it != range.second; ++it)
+      if (memcmp(it->second.key, &key, sizeof(key)) == 0) { memcpy(out, it->second.map, sizeof(CUtensorMap)); return HB_OK; }
+  }
   cuuint64_t gdims[5];
   cuuint64_t gstr[5];
   cuuint32_t gbox[5], estr[5];
@@ -215,6 +240,15 @@ hb_status hb_make_tensor_map(hb_ctx* ctx, CUtensorMap* out, CUtensorMapDataType 
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return hb_fail(ctx, HB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  if (ctx) {
+    if (ctx->tmap_cache.size() >= 8192) ctx->tmap_cache.clear();      // bounded: start over rather than grow
+    hb_tmap_entry e;
+    static_assert(sizeof(e.key) >= sizeof(hb_tmap_key), "tensor-map cache key storage");
+    memset(&e, 0, sizeof(e));
+    memcpy(e.key, &key, sizeof(key));
+    memcpy(e.map, out, sizeof(CUtensorMap));
+    ctx->tmap_cache.emplace(h, e);
+  }
   return HB_OK;
 }
 

@@ -9,7 +9,7 @@ from . import _capi
 from .model_ir import Context, Tensor, _contig, _lib
 
 (NODE_MATMUL, NODE_ATTENTION, NODE_ALL_REDUCE, NODE_RMSNORM, NODE_ROPE, NODE_EMBEDDING, NODE_SWIGLU, NODE_GELU,
- NODE_ADD, NODE_ARGMAX, NODE_AR_NORM) = range(11)
+ NODE_ADD, NODE_ARGMAX, NODE_AR_NORM, NODE_ROPE_APPEND, NODE_ATTN_DECODE, NODE_ADVANCE) = range(14)
 T_SYMMETRIC = 1
 
 
@@ -88,6 +88,18 @@ class Graph:
     def rope(self, x, seq, heads, head_dim, base=10000.0, pos0=0):
         return self._add(NODE_ROPE, [], x, [seq, heads, head_dim, pos0], [base])
 
+    def rope_append(self, qkv, pos, kv_cache, n_q_heads, n_kv_heads, base=10000.0):
+        """RoPE of the new token's q and k heads at pos[0] (in place) and append of k, v to the cache."""
+        return self._add(NODE_ROPE_APPEND, [qkv, pos], kv_cache, [n_q_heads, n_kv_heads], [base])
+
+    def attention_decode(self, qkv, kv_cache, pos, out, n_q_heads, n_kv_heads, scale=None, len_hint=0):
+        if scale is None:
+            scale = float(self.meta[kv_cache][1][-1]) ** -0.5
+        return self._add(NODE_ATTN_DECODE, [qkv, kv_cache, pos], out, [n_q_heads, n_kv_heads, len_hint], [scale])
+
+    def advance(self, pos, n=1):
+        return self._add(NODE_ADVANCE, [], pos, [n])
+
     def embedding(self, table, ids, out):
         return self._add(NODE_EMBEDDING, [table, ids], out)
 
@@ -111,6 +123,14 @@ class Graph:
 
     def run(self):
         self.ctx._check(_lib.hb_graph_run(self._h))
+
+    def capture(self):
+        """Record one run of the planned graph into a CUDA graph (after one eager run)."""
+        self.ctx._check(_lib.hb_graph_capture(self._h))
+
+    def replay(self):
+        """Enqueue the captured step with a single call."""
+        self.ctx._check(_lib.hb_graph_replay(self._h))
 
     def run_timed(self, n_nodes: int):
         """One run with per-node device timing; returns a list of milliseconds."""

@@ -209,6 +209,29 @@ class Context:
             out.ctypes.data_as(C.c_void_p), B, S, Hq, Hkv, D, int(causal), scale))
         return out
 
+    # -- decode-shaped path ----------------------------------------------------------
+    def rope_append(self, qkv: Tensor, kv_cache: Tensor, pos: Tensor, n_q_heads: int, n_kv_heads: int,
+                    base: float = 10000.0):
+        """RoPE of the new token's q and k heads at position pos[0] (in place in `qkv`
+        [batch, row]) and append of k and v to `kv_cache` [2*batch, s_max, kv_heads, 128]."""
+        self._check(_lib.hb_rope_append(self._h, qkv.ptr, qkv.stride[0], kv_cache.ptr, pos.ptr, qkv.shape[0], n_q_heads,
+                                        n_kv_heads, kv_cache.shape[3], kv_cache.shape[1], base))
+
+    def attention_decode(self, qkv: Tensor, kv_cache: Tensor, pos: Tensor, n_q_heads: int, n_kv_heads: int,
+                         out: Optional[Tensor] = None, scale: Optional[float] = None, len_hint: int = 0) -> Tensor:
+        """Single-query attention of each sequence's new token over cache positions 0..pos[0]."""
+        D = kv_cache.shape[3]
+        if out is None:
+            out = self.empty((qkv.shape[0], n_q_heads * D))
+        if scale is None:
+            scale = float(D) ** -0.5
+        self._check(_lib.hb_attention_decode(self._h, qkv.ptr, qkv.stride[0], kv_cache.ptr, pos.ptr, out.ptr, qkv.shape[0],
+                                             n_q_heads, n_kv_heads, D, kv_cache.shape[1], len_hint, scale))
+        return out
+
+    def advance_pos(self, pos: Tensor, n: int = 1):
+        self._check(_lib.hb_advance_pos(self._h, pos.ptr, n))
+
     # -- glue ---------------------------------------------------------------------
     def rmsnorm(self, x: Tensor, gain: Tensor, out: Optional[Tensor] = None, eps: float = 1e-5,
                 residual: Optional[Tensor] = None) -> Tensor:

@@ -239,3 +239,100 @@ class DecoderGraph:
 
     def run(self):
         self.graph.run()
+
+
+def decode_layer(full: Dict[str, np.ndarray], cfg: DecoderConfig) -> Dict[str, np.ndarray]:
+    """One layer's weights in the form the decode graph wants (single rank): wqkv
+    [(Hq+2Hkv)*hd, d], wo [d, Hq*hd], wgu [2F, d] with the F gate rows first and the F up rows
+    second (the stand-alone SwiGLU kernel reads the two halves), wd [d, F], and the gains."""
+    return {"wqkv": np.ascontiguousarray(np.concatenate([full["wq"], full["wk"], full["wv"]], 0)),
+            "wo": np.ascontiguousarray(full["wo"]), "wgu": np.ascontiguousarray(np.concatenate([full["wg"], full["wu"]], 0)),
+            "wd": np.ascontiguousarray(full["wd"]), "g1": full["g1"], "g2": full["g2"]}
+
+
+class DecodeGraph:
+    """One generation step of the decoder block for `batch` sequences on one GPU: the new
+    token's embedding in, its output row out, key/value caches of `s_max` positions per layer.
+    The projections are M = batch products (the stream-K kernel for M <= 64), attention is the
+    split-KV single-query kernel, and the position is a device-side counter that the last node
+    advances, so every step enqueues exactly the same launches (``advance=False`` keeps the
+    position fixed: the benchmark's steady-state step)."""
+
+    def __init__(self, ctx, cfg: DecoderConfig, layers: List[Dict[str, np.ndarray]], batch: int, s_max: int,
+                 advance: bool = True, len_hint: int = 0):
+        from .graph import Graph
+        self.ctx, self.cfg, self.batch, self.s_max = ctx, cfg, batch, s_max
+        d, hd, Hq, Hkv, F = cfg.d_model, cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads, cfg.ffn_hidden
+        W = (Hq + 2 * Hkv) * hd
+        B = batch
+        g = self.graph = Graph(ctx)
+        self.x = ctx.empty((B, d))
+        self.out = ctx.empty((B, d))
+        self.pos = ctx.upload(np.zeros(1, np.int32))
+        self.kv = [ctx.empty((2 * B, s_max, Hkv, hd)) for _ in layers]
+        x_in, out, pos = g.input(self.x), g.input(self.out), g.input(self.pos)
+        self.weights = [{k: ctx.upload(v) for k, v in lw.items()} for lw in layers]
+        ws = [{k: g.input(v if k in ("g1", "g2") else v.T) for k, v in dev.items()} for dev in self.weights]
+        xres = g.temp((B, d))                 # residual stream
+        pending = None                        # sublayer output not yet added into the stream
+        for li, w in enumerate(ws):
+            kv = g.input(self.kv[li])
+            h = g.temp((B, d))
+            if li == 0:
+                g.rmsnorm(x_in, w["g1"], h, eps=cfg.eps)
+            else:
+                g.rmsnorm(pending, w["g1"], h, residual=xres, eps=cfg.eps)
+            qkv = g.temp((B, W))
+            g.matmul(h, w["wqkv"], qkv)
+            g.rope_append(qkv, pos, kv, Hq, Hkv, cfg.rope_base)
+            attn = g.temp((B, Hq * hd))
+            g.attention_decode(qkv, kv, pos, attn, Hq, Hkv, len_hint=len_hint)
+            ao = g.temp((B, d))
+            g.matmul(attn, w["wo"], ao)
+            h2 = g.temp((B, d))
+            if li == 0:
+                g.add(x_in, ao, xres)
+                g.rmsnorm(xres, w["g2"], h2, eps=cfg.eps)
+            else:
+                g.rmsnorm(ao, w["g2"], h2, residual=xres, eps=cfg.eps)
+            gu = g.temp((B, 2 * F))
+            g.matmul(h2, w["wgu"], gu)
+            act = g.temp((B, F))
+            g.swiglu(gu, act)
+            fo = g.temp((B, d))
+            g.matmul(act, w["wd"], fo)
+            pending = fo
+        g.add(xres, pending, out)
+        if advance:
+            g.advance(pos, 1)
+        self.arena, _ = g.plan()
+        self.captured = False
+
+    def set_pos(self, pos: int):
+        import ctypes as C
+        from .model_ir import _lib
+        a = np.array([pos], np.int32)
+        self.ctx._check(_lib.hb_upload(self.ctx._h, C.c_void_p(self.pos.ptr), a.ctypes.data_as(C.c_void_p), 4))
+        self.ctx.sync()
+
+    def step(self):
+        if self.captured:
+            self.graph.replay()
+        else:
+            self.graph.run()
+
+    def capture(self):
+        """Replay from now on: one eager step first (it sizes the scratch buffers and, like any
+        step, advances the position), then the capture."""
+        self.graph.run()
+        self.ctx.sync()
+        self.graph.capture()
+        self.captured = True
+
+    def bytes_per_step(self, length: int) -> float:
+        """Algorithmic HBM bytes of one step at cache length `length`: every weight once, the
+        cached keys and values of every layer once."""
+        cfg = self.cfg
+        w = sum(t.nbytes for dev in self.weights for k, t in dev.items())
+        kvb = len(self.kv) * 2.0 * self.batch * length * cfg.n_kv_heads * cfg.head_dim * 2
+        return w + kvb

@@ -142,6 +142,34 @@ hb_status hb_attention_host(hb_ctx* ctx, const void* Q, const void* K, const voi
                             int64_t n_kv_heads, int64_t head_dim, int32_t causal,
                             float scale);
 
+/* ---- decode-shaped path: one new token per sequence against a key/value cache --------
+ * Cache: kv_cache[2 * batch, s_max, n_kv_heads, 128] bf16 -- keys in the first `batch`
+ * entries, values in the second, token-major like the attention node's tensors.  `qkv` is
+ * the new token's projection, one row per sequence: q heads, then k heads, then v heads
+ * (row_stride elements per row).  `pos_dev` is a DEVICE int32: the position of the new token
+ * (the cache then holds pos + 1 tokens), shared by all sequences; keeping it on the device
+ * makes every step's launches identical, so a planned step can be captured and replayed.
+ * No reference counterpart (the reference has no attention at all).
+ *   hb_rope_append       rotate-half RoPE of the q and k heads at *pos_dev, in place (same
+ *                        angles as hb_rope: theta_i = base^(-2i/128), formed in double), and
+ *                        append of the rotated k heads and the v heads to the cache.  A full
+ *                        cache (*pos_dev >= s_max) writes nothing and makes the next hb_sync
+ *                        return HB_ERR_INVALID.
+ *   hb_attention_decode  out[batch, n_q_heads * 128] = softmax(scale * q K^T) V over cache
+ *                        positions 0..*pos_dev, fp32 scores / max / sum; grouped-query heads
+ *                        share one pass over their KV head.  The positions are split over
+ *                        CTAs (len_hint: expected length, used only to size the splits; 0 =
+ *                        s_max) and merged in a fixed order: bit-identical run to run.
+ *   hb_advance_pos       *pos_dev += n. */
+hb_status hb_rope_append(hb_ctx* ctx, void* qkv, int64_t row_stride, void* kv_cache,
+                         const int32_t* pos_dev, int64_t batch, int64_t n_q_heads,
+                         int64_t n_kv_heads, int64_t head_dim, int64_t s_max, float base);
+hb_status hb_attention_decode(hb_ctx* ctx, const void* qkv, int64_t row_stride,
+                              const void* kv_cache, const int32_t* pos_dev, void* out,
+                              int64_t batch, int64_t n_q_heads, int64_t n_kv_heads,
+                              int64_t head_dim, int64_t s_max, int64_t len_hint, float scale);
+hb_status hb_advance_pos(hb_ctx* ctx, int32_t* pos_dev, int32_t n);
+
 /* ---- glue operators the decoder / MLP configurations put on the path ------------- */
 /* y = x * rsqrt(mean(x^2) + eps) * gain; rows x cols bf16, gain bf16[cols]. If
  * `residual_inout` is non-NULL it is first updated in place: residual += x, and the
@@ -240,8 +268,13 @@ enum {
   HB_NODE_GELU = 7,        /* in: x */
   HB_NODE_ADD = 8,         /* in: a, b */
   HB_NODE_ARGMAX = 9,      /* in: x */
-  HB_NODE_AR_NORM = 10     /* in: partial, [gain], residual_in, residual_out (written); out: normalised
+  HB_NODE_AR_NORM = 10,    /* in: partial, [gain], residual_in, residual_out (written); out: normalised
                               or gathered rows   iparam: mode, algorithm   fparam: eps */
+  HB_NODE_ROPE_APPEND = 11,  /* in: qkv [batch, row] (rotated in place), pos (i32[1]); out: kv cache
+                                [2*batch, s_max, kv_heads, 128]   iparam: q heads, kv heads   fparam: base */
+  HB_NODE_ATTN_DECODE = 12,  /* in: qkv, kv cache, pos; out: [batch, q_heads*128]
+                                iparam: q heads, kv heads, len_hint   fparam: scale */
+  HB_NODE_ADVANCE = 13       /* in place on `out` (i32[1])   iparam: increment */
 };
 enum { HB_T_SYMMETRIC = 1 };
 typedef struct hb_node {
@@ -275,6 +308,16 @@ hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* symmetric_byte
 hb_status hb_plan_arena(int32_t n, const size_t* bytes, const int32_t* first, const int32_t* last,
                         size_t* offsets, size_t* total);
 hb_status hb_graph_run(hb_graph* g);
+/* Replay: hb_graph_capture records one run of the planned graph (both streams and the event
+ * edges between them) into a CUDA graph; hb_graph_replay enqueues that whole step on the
+ * context's stream with one call.  The graph must have run once through hb_graph_run since it
+ * was planned (scratch buffers reach their size on first use); everything read from the host --
+ * addresses, shapes, configuration choices -- is frozen at capture time, so per-step values
+ * must live in device memory (the decode position does); hb_graph_plan drops the capture.
+ * Graphs with collective nodes on more than one rank are refused (HB_ERR_UNSUPPORTED).
+ * No reference counterpart. */
+hb_status hb_graph_capture(hb_graph* g);
+hb_status hb_graph_replay(hb_graph* g);
 /* One run with a CUDA event between nodes: ms[i] = device time of node i (first n nodes). */
 hb_status hb_graph_run_timed(hb_graph* g, float* ms, int32_t n);
 hb_status hb_graph_describe(hb_graph* g, char* buf, size_t len);

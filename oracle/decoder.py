@@ -63,3 +63,49 @@ def forward(cfg, x0, layers, round_bf16=True, heads=None, ffn=None, reduce=None,
         fo = reduce(rnd(oracle.gemm(act, np.ascontiguousarray(lw["wd"][:, f0:f1]).T)))
         x = rnd_x(x + rnd(fo))
     return x
+
+
+def new_cache(cfg, batch, s_max):
+    """Per layer: (K, V), each [batch, s_max, n_kv_heads, head_dim] fp32, zero-filled."""
+    return [(np.zeros((batch, s_max, cfg.n_kv_heads, cfg.head_dim), np.float32),
+             np.zeros((batch, s_max, cfg.n_kv_heads, cfg.head_dim), np.float32)) for _ in range(cfg.n_layers)]
+
+
+def decode_step(cfg, x_t, layers, cache, pos, round_bf16=True):
+    """One generation step: x_t [batch, d_model] are the new tokens' embeddings at position
+    `pos` of every sequence; `cache` (from :func:`new_cache`) holds the rotated keys and the
+    values of positions < pos and receives those of `pos`.  Same definitions as :func:`forward`
+    (the step for token t reproduces row t of the prefill forward of the same sequence); in
+    bf16-storage mode the roundings sit where the device's decode graph stores bf16: gate and up
+    projections are rounded before SwiGLU (a stand-alone kernel there), the residual stream after
+    every add."""
+    rnd = (lambda a: oracle.round_bf16(np.ascontiguousarray(a, np.float32))) if round_bf16 else (lambda a: np.ascontiguousarray(a, np.float32))
+    hd, Hq, Hkv = cfg.head_dim, cfg.n_q_heads, cfg.n_kv_heads
+    B = x_t.shape[0]
+    G = Hq // Hkv
+    x = x_t.astype(np.float32)
+    scale = np.float32(1.0 / np.sqrt(hd))
+    for lw, (Kc, Vc) in zip(layers, cache):
+        h = rnd(oracle.rmsnorm(x, lw["g1"], cfg.eps))
+        q = rnd(oracle.gemm(h, lw["wq"].T))
+        k = rnd(oracle.gemm(h, lw["wk"].T))
+        v = rnd(oracle.gemm(h, lw["wv"].T))
+        q = rnd(oracle.rope(q, 1, Hq, hd, cfg.rope_base, pos0=pos))       # one token per row, all at position pos
+        k = rnd(oracle.rope(k, 1, Hkv, hd, cfg.rope_base, pos0=pos))
+        Kc[:, pos] = k.reshape(B, Hkv, hd)
+        Vc[:, pos] = v.reshape(B, Hkv, hd)
+        L = pos + 1
+        qh = q.reshape(B, Hkv, G, hd)
+        s = np.einsum("bkgd,blkd->bkgl", qh, Kc[:, :L], dtype=np.float32) * scale
+        s = s - s.max(-1, keepdims=True)
+        p = np.exp(s, dtype=np.float32)
+        p = p / p.sum(-1, keepdims=True)
+        a = rnd(np.einsum("bkgl,blkd->bkgd", p, Vc[:, :L], dtype=np.float32).reshape(B, Hq * hd))
+        ao = rnd(oracle.gemm(a, lw["wo"].T))
+        x = rnd(x + ao)
+        h2 = rnd(oracle.rmsnorm(x, lw["g2"], cfg.eps))
+        gu = np.concatenate([rnd(oracle.gemm(h2, lw["wg"].T)), rnd(oracle.gemm(h2, lw["wu"].T))], 1)
+        act = rnd(oracle.swiglu(gu))
+        fo = rnd(oracle.gemm(act, lw["wd"].T))
+        x = rnd(x + fo)
+    return x
