@@ -493,6 +493,12 @@ extern "C" hb_status hb_attention(hb_ctx* ctx, const hb_tensor* Q, const hb_tens
   // variable HB_ATTN_PERSISTENT=0/1 overrides.  Each launch takes the next of a few work
   // counters so that launches in flight on different streams never share one.
   bool persist = units >= 2 * (int64_t)ctx->sm_count;
+  if (opts->config_id == 0 || opts->config_id == 1) {
+    persist = opts->config_id == 1;                       // the caller's choice (the autotuner's candidates)
+  } else {
+    const int cached = hb_attention_cached_choice(ctx, B, S, Hq, Hkv, opts->causal ? 1 : 0);
+    if (cached == 0 || cached == 1) persist = cached == 1;
+  }
   if (const char* e = getenv("HB_ATTN_PERSISTENT")) persist = atoi(e) != 0;
   p.work_counter = nullptr;
   if (persist) {

@@ -260,6 +260,8 @@ hb_allreduce_nvls_kernel(const ArParams p, char* mc) {
   ar_barrier(p, 1, cta);
 }
 
+void comm_kernel_setup(hb_ctx* ctx);   // defined after the fused kernels below
+
 }  // namespace
 
 extern "C" hb_status hb_comm_unique_id(void* id_out) {
@@ -451,6 +453,7 @@ extern "C" hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32
   p.epoch = ++s.epoch;
   p.spin_limit = s.spin_limit;
   p.status = ctx->d_status;
+  comm_kernel_setup(ctx);
   const int64_t nvec = count / (16 / es);
   int64_t want = (nvec / s.world + AR_THREADS - 1) / AR_THREADS;
   int grid = (int)(want < 1 ? 1 : want);
@@ -509,6 +512,7 @@ struct ArnParams {
   int rows, cols8;
   float inv_cols, eps;
   int mode;
+  int stagger;                 // rows kernel: pace warps 4..7 behind warps 0..3 (in-switch form)
 };
 
 template <bool NVLS, int WORLD>
@@ -641,15 +645,34 @@ constexpr int ARW_VEC = 16;    // 16-byte vectors per lane: cols <= 32 * 16 * 8 
 template <bool NVLS, int WORLD>
 __global__ void __launch_bounds__(AR_THREADS, 1)
 hb_allreduce_norm_rows_kernel(const ArnParams p) {
+  // Pacing between the two halves of the CTA (see `stagger` below).
+  __shared__ volatile int loaded[AR_THREADS / 64];
   const int cta = blockIdx.x;
+  if (threadIdx.x < AR_THREADS / 64) loaded[threadIdx.x] = 0;
   if (!ar_barrier(p.ar, 0, cta)) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int per = p.rows / p.ar.world;
   const int row0 = per * p.ar.rank;
   const int nwarps = gridDim.x * (AR_THREADS / 32);
-  for (int row = row0 + cta * (AR_THREADS / 32) + warp; row < row0 + per; row += nwarps) {
+  // In the in-switch form the two phases of a row load opposite directions of the link: the
+  // reduction pulls every rank's copy of the row through this GPU's outgoing lanes (world x the
+  // bytes it receives), the broadcast store fans out into every GPU's incoming lanes.  Warps that
+  // all read and then all write use one direction at a time.  With `stagger` warps 4..7 start a
+  // row's reads only when their partner (warp - 4) has received the reads of the same round, so
+  // one half of the CTA reads while the other half writes.  The pacing is a hint, not a
+  // dependency: a wait that runs out simply proceeds.
+  const bool follower = p.stagger && warp >= AR_THREADS / 64;
+  const int pair_slot = warp & (AR_THREADS / 64 - 1);
+  int round = 0;
+  for (int row = row0 + cta * (AR_THREADS / 32) + warp; row < row0 + per; row += nwarps, ++round) {
     const int64_t base = static_cast<int64_t>(row) * p.cols8;
     uint4 s[ARW_VEC];
+    if (follower) {
+      if (lane == 0) {
+        for (int it = 0; loaded[pair_slot] <= round && it < (1 << 16); ++it) __nanosleep(64);
+      }
+      __syncwarp();
+    }
     if (NVLS) {
 #pragma unroll
       for (int k = 0; k < ARW_VEC; ++k) {
@@ -699,6 +722,7 @@ hb_allreduce_norm_rows_kernel(const ArnParams p) {
         p.residual_out[base + c] = s[k];
       }
     }
+    if (p.stagger && !follower && lane == 0) loaded[pair_slot] = round + 1;   // this round's reads have landed
     float inv = 1.0f;
     if (p.mode == 0) {
       float tot = 0.f;
@@ -739,7 +763,34 @@ hb_allreduce_norm_rows_kernel(const ArnParams p) {
       }
     }
   }
+  if (p.stagger && !follower && lane == 0) loaded[pair_slot] = 1 << 30;   // no more rounds: followers run free
   ar_barrier(p.ar, 1, cta);
+}
+
+// The collective kernels use almost no shared memory, the GEMM and attention kernels they
+// run beside use nearly all of it.  An SM holds CTAs of two kernels at the same time only if
+// both were launched with the same split between L1 and shared memory, so the collective
+// kernels ask for the largest shared-memory carve-out too (HB_AR_CARVEOUT=0 leaves the
+// driver's choice).
+template <typename K>
+void prefer_max_shared(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+void comm_kernel_setup(hb_ctx* ctx) {
+  static bool done[64] = {};
+  if (done[ctx->device & 63]) return;
+  done[ctx->device & 63] = true;
+  if (const char* e = getenv("HB_AR_CARVEOUT"))
+    if (atoi(e) == 0) return;
+  prefer_max_shared(hb_allreduce_p2p_kernel<float, 2>); prefer_max_shared(hb_allreduce_p2p_kernel<float, 4>);
+  prefer_max_shared(hb_allreduce_p2p_kernel<float, 8>); prefer_max_shared(hb_allreduce_p2p_kernel<__nv_bfloat16, 2>);
+  prefer_max_shared(hb_allreduce_p2p_kernel<__nv_bfloat16, 4>); prefer_max_shared(hb_allreduce_p2p_kernel<__nv_bfloat16, 8>);
+  prefer_max_shared(hb_allreduce_nvls_kernel<float>); prefer_max_shared(hb_allreduce_nvls_kernel<__nv_bfloat16>);
+  prefer_max_shared(hb_allreduce_norm_kernel<true, 1>); prefer_max_shared(hb_allreduce_norm_kernel<false, 2>);
+  prefer_max_shared(hb_allreduce_norm_kernel<false, 4>); prefer_max_shared(hb_allreduce_norm_kernel<false, 8>);
+  prefer_max_shared(hb_allreduce_norm_rows_kernel<true, 1>); prefer_max_shared(hb_allreduce_norm_rows_kernel<false, 2>);
+  prefer_max_shared(hb_allreduce_norm_rows_kernel<false, 4>); prefer_max_shared(hb_allreduce_norm_rows_kernel<false, 8>);
+  cudaGetLastError();
 }
 
 }  // namespace
@@ -786,17 +837,23 @@ extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const 
   p.inv_cols = 1.0f / (float)cols;
   p.eps = eps;
   p.mode = mode;
+  comm_kernel_setup(ctx);
   bool by_rows = cols <= 32 * ARW_VEC * 8;            // warp-per-row form
   if (const char* e = getenv("HB_ARN_ROWS")) by_rows = by_rows && atoi(e) != 0;
   if (by_rows) {
     const int per = (int)(rows / s.world);
     int grid = (per + AR_THREADS / 32 - 1) / (AR_THREADS / 32);
     int cap = ctx->sm_count < AR_MAX_CTAS ? ctx->sm_count : AR_MAX_CTAS;
-    if (const char* e = getenv("HB_AR_MAX_CTAS")) {   // every rank must use the same value
+    if (const char* e = getenv("HB_ARN_CTAS")) {      // every rank must use the same value
+      const int v = atoi(e);
+      if (v >= 1 && v < cap) cap = v;
+    } else if (const char* e = getenv("HB_AR_MAX_CTAS")) {
       const int v = atoi(e);
       if (v >= 1 && v < cap) cap = v;
     }
     if (grid > cap) grid = cap;
+    p.stagger = algo == HB_AR_NVLS ? 1 : 0;
+    if (const char* e = getenv("HB_ARN_STAGGER")) p.stagger = atoi(e) != 0;
     if (algo == HB_AR_NVLS) hb_allreduce_norm_rows_kernel<true, 1><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
     else if (s.world == 2) hb_allreduce_norm_rows_kernel<false, 2><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
     else if (s.world <= 4) hb_allreduce_norm_rows_kernel<false, 4><<<grid, AR_THREADS, 0, ctx->stream>>>(p);

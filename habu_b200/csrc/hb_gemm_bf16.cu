@@ -41,10 +41,14 @@ struct GemmParams {
   int32_t* status;
 };
 
-template <int BN, int STAGES>
+// A ring stage holds KPS consecutive 64-wide k-blocks of both operands (KPS = 2: a 128-wide
+// K step per barrier round trip, half as many producer/consumer hand-offs).
+template <int BN, int STAGES, int KPS>
 struct SmemLayout {
-  static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int A_BLOCK = BM * BK * 2;
+  static constexpr int B_BLOCK = BN * BK * 2;
+  static constexpr int A_BYTES = KPS * A_BLOCK;
+  static constexpr int B_BYTES = KPS * B_BLOCK;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_BAR = OFF_B + STAGES * B_BYTES;
@@ -143,11 +147,11 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, bool vec_ok,
     }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KPS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, KPS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -191,7 +195,7 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_kb = (p.K + BK * KPS - 1) / (BK * KPS);   // ring steps per tile; a block past K loads zeros
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -206,21 +210,25 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(bar_empty + s * 8, phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_arrive_expect_tx(bar_full + s * 8, L::A_BYTES + L::B_BYTES);
-          const int k0 = kb * BK;
-          if (!p.a_mn) {
-            tma_load_2d(sA + s * L::A_BYTES, &tmA, bar_full + s * 8, k0, m0);
-          } else {
-            // M-major A: two boxes of 64 (M) x 64 (K); box c holds rows m0+64c..+63
-            tma_load_2d(sA + s * L::A_BYTES, &tmA, bar_full + s * 8, m0, k0);
-            tma_load_2d(sA + s * L::A_BYTES + L::A_BYTES / 2, &tmA, bar_full + s * 8, m0 + 64, k0);
-          }
-          if (!p.b_mn) {
-            tma_load_2d(sB + s * L::B_BYTES, &tmB, bar_full + s * 8, k0, n0);
-          } else {
 #pragma unroll
-            for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sB + s * L::B_BYTES + c * (64 * BK * 2), &tmB, bar_full + s * 8,
-                          n0 + 64 * c, k0);
+          for (int kk = 0; kk < KPS; ++kk) {
+            const int k0 = (kb * KPS + kk) * BK;
+            const uint32_t a_dst = sA + s * L::A_BYTES + kk * L::A_BLOCK;
+            const uint32_t b_dst = sB + s * L::B_BYTES + kk * L::B_BLOCK;
+            if (!p.a_mn) {
+              tma_load_2d(a_dst, &tmA, bar_full + s * 8, k0, m0);
+            } else {
+              // M-major A: two boxes of 64 (M) x 64 (K); box c holds rows m0+64c..+63
+              tma_load_2d(a_dst, &tmA, bar_full + s * 8, m0, k0);
+              tma_load_2d(a_dst + L::A_BLOCK / 2, &tmA, bar_full + s * 8, m0 + 64, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d(b_dst, &tmB, bar_full + s * 8, k0, n0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BN / 64; ++c)
+                tma_load_2d(b_dst + c * (64 * BK * 2), &tmB, bar_full + s * 8, n0 + 64 * c, k0);
+            }
           }
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
@@ -244,17 +252,20 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(bar_full + s * 8, phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = sA + s * L::A_BYTES;
-          const uint32_t b_addr = sB + s * L::B_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            // K-major: 16 bf16 = 32 bytes further along the 128-byte swizzled row.
-            // MN-major: 16 k-rows = two 8-row groups of 1024 bytes further.
-            const uint64_t ad = p.a_mn ? umma_desc_mn_sw128(a_addr + k * 2048, L::A_BYTES / 2, 1024)
-                                       : umma_desc_k_sw128(a_addr + k * 32);
-            const uint64_t bd = p.b_mn ? umma_desc_mn_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
-                                       : umma_desc_k_sw128(b_addr + k * 32);
-            umma_ss<1>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < KPS; ++kk) {
+            const uint32_t a_addr = sA + s * L::A_BYTES + kk * L::A_BLOCK;
+            const uint32_t b_addr = sB + s * L::B_BYTES + kk * L::B_BLOCK;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // K-major: 16 bf16 = 32 bytes further along the 128-byte swizzled row.
+              // MN-major: 16 k-rows = two 8-row groups of 1024 bytes further.
+              const uint64_t ad = p.a_mn ? umma_desc_mn_sw128(a_addr + k * 2048, L::A_BLOCK / 2, 1024)
+                                         : umma_desc_k_sw128(a_addr + k * 32);
+              const uint64_t bd = p.b_mn ? umma_desc_mn_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
+                                         : umma_desc_k_sw128(b_addr + k * 32);
+              umma_ss<1>(d_tmem, ad, bd, idesc, (kb | kk | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit<1>(bar_empty + s * 8);
           if (++s == STAGES) { s = 0; phase ^= 1; }
@@ -317,10 +328,16 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 //   tfull[a]   one per CTA, same way;   tempty[a]  leader only, 256 arrivals (both epilogues)
 // No load is multicast: each CTA fetches exactly the bytes it owns.
 // ------------------------------------------------------------------------------------
-template <int STAGES>
+// BN2 is the width of the pair's tile (256 x BN2, BN2 = 256 or 128): each CTA holds 128 rows of
+// A and BN2 / 2 rows of B per k-block.  The narrower tile gives three times as many tiles on
+// short-N products (a 768-wide QKV shard), where 256 x 256 tiles leave a third of the last wave
+// empty.
+template <int BN2, int STAGES, int KPS>
 struct SmemLayout2 {
-  static constexpr int A_BYTES = 128 * BK * 2;
-  static constexpr int B_BYTES = 128 * BK * 2;
+  static constexpr int A_BLOCK = 128 * BK * 2;
+  static constexpr int B_BLOCK = (BN2 / 2) * BK * 2;
+  static constexpr int A_BYTES = KPS * A_BLOCK;
+  static constexpr int B_BYTES = KPS * B_BLOCK;
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_BAR = OFF_B + STAGES * B_BYTES;
@@ -331,12 +348,12 @@ struct SmemLayout2 {
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
 
-template <int STAGES>
+template <int BN2, int STAGES, int KPS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const GemmParams p) {
-  using L = SmemLayout2<STAGES>;
-  constexpr int BN2 = 256;
+  using L = SmemLayout2<BN2, STAGES, KPS>;
+  constexpr uint32_t TMEM_COLS = 2 * BN2;          // two accumulators: 512 or 256 columns
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -372,7 +389,7 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {   // the same warp in both CTAs, same destination address
-    tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), 512);
+    tmem_alloc<2>(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), TMEM_COLS);
     tmem_relinquish<2>();
   }
   tc_fence_before();
@@ -380,8 +397,8 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;     // 256 x 256 tiles
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_tiles = p.tiles_m * p.tiles_n;     // 256 x BN2 tiles
+  const int num_kb = (p.K + BK * KPS - 1) / (BK * KPS);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -393,23 +410,30 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         int tm, tn;
         tile_coords(tile, p, tm, tn);
         const int m0 = tm * 256 + static_cast<int>(cta_rank) * 128;
-        const int n0 = tn * BN2 + static_cast<int>(cta_rank) * 128;
+        const int n0 = tn * BN2 + static_cast<int>(cta_rank) * (BN2 / 2);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(bar_empty + s * 8, phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t full_leader = mapa(bar_full + s * 8, 0);
           if (leader) mbar_arrive_expect_tx(bar_full + s * 8, L::A_BYTES + L::B_BYTES);
           else mbar_arrive_expect_tx_cluster(full_leader, L::A_BYTES + L::B_BYTES);
-          if (!p.a_mn) {
-            tma_load_2d_pair(sA + s * L::A_BYTES, &tmA, full_leader, kb * BK, m0);
-          } else {   // M-major A: two boxes of 64 (M) x 64 (K)
-            tma_load_2d_pair(sA + s * L::A_BYTES, &tmA, full_leader, m0, kb * BK);
-            tma_load_2d_pair(sA + s * L::A_BYTES + L::A_BYTES / 2, &tmA, full_leader, m0 + 64, kb * BK);
-          }
-          if (!p.b_mn) {
-            tma_load_2d_pair(sB + s * L::B_BYTES, &tmB, full_leader, kb * BK, n0);
-          } else {   // N-major B: two boxes of 64 (N) x 64 (K)
-            tma_load_2d_pair(sB + s * L::B_BYTES, &tmB, full_leader, n0, kb * BK);
-            tma_load_2d_pair(sB + s * L::B_BYTES + L::B_BYTES / 2, &tmB, full_leader, n0 + 64, kb * BK);
+#pragma unroll
+          for (int kk = 0; kk < KPS; ++kk) {
+            const int k0 = (kb * KPS + kk) * BK;
+            const uint32_t a_dst = sA + s * L::A_BYTES + kk * L::A_BLOCK;
+            const uint32_t b_dst = sB + s * L::B_BYTES + kk * L::B_BLOCK;
+            if (!p.a_mn) {
+              tma_load_2d_pair(a_dst, &tmA, full_leader, k0, m0);
+            } else {   // M-major A: two boxes of 64 (M) x 64 (K)
+              tma_load_2d_pair(a_dst, &tmA, full_leader, m0, k0);
+              tma_load_2d_pair(a_dst + L::A_BLOCK / 2, &tmA, full_leader, m0 + 64, k0);
+            }
+            if (!p.b_mn) {
+              tma_load_2d_pair(b_dst, &tmB, full_leader, k0, n0);
+            } else {   // N-major B: boxes of 64 (N) x 64 (K)
+#pragma unroll
+              for (int c = 0; c < BN2 / 128; ++c)
+                tma_load_2d_pair(b_dst + c * (64 * BK * 2), &tmB, full_leader, n0 + 64 * c, k0);
+            }
           }
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
@@ -434,13 +458,16 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           if (!mbar_wait(bar_full + s * 8, phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint32_t a_addr = sA + s * L::A_BYTES, b_addr = sB + s * L::B_BYTES;
-            const uint64_t ad = p.a_mn ? umma_desc_mn_sw128(a_addr + k * 2048, L::A_BYTES / 2, 1024)
-                                       : umma_desc_k_sw128(a_addr + k * 32);
-            const uint64_t bd = p.b_mn ? umma_desc_mn_sw128(b_addr + k * 2048, L::B_BYTES / 2, 1024)
-                                       : umma_desc_k_sw128(b_addr + k * 32);
-            umma_ss<2>(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int kk = 0; kk < KPS; ++kk) {
+            const uint32_t a_addr = sA + s * L::A_BYTES + kk * L::A_BLOCK, b_addr = sB + s * L::B_BYTES + kk * L::B_BLOCK;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t ad = p.a_mn ? umma_desc_mn_sw128(a_addr + k * 2048, L::A_BLOCK / 2, 1024)
+                                         : umma_desc_k_sw128(a_addr + k * 32);
+              const uint64_t bd = p.b_mn ? umma_desc_mn_sw128(b_addr + k * 2048, 64 * BK * 2, 1024)
+                                         : umma_desc_k_sw128(b_addr + k * 32);
+              umma_ss<2>(d_tmem, ad, bd, idesc, (kb | kk | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit_pair_mcast(bar_empty + s * 8, 3);      // frees the slot in both CTAs
           if (++s == STAGES) { s = 0; phase ^= 1; }
@@ -485,29 +512,36 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   cluster_sync();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<2>(tmem_base, 512);
+    tmem_dealloc<2>(tmem_base, TMEM_COLS);
   }
 }
 
-struct GemmConfig {
-  int bn, stages;
-  int raster_group;
-  int cluster;      // 1: one CTA per 128 x bn tile; 2: CTA pair per 256 x 256 tile
+struct GemmVariant {
+  int cluster;      // 1: one CTA per 128 x bn tile; 2: CTA pair per 256 x bn tile
+  int bn;           // tile N
+  int stages;       // ring depth
+  int kps;          // 64-wide k-blocks per ring stage (tile K = 64 * kps)
 };
-// config_id -> (tile N, stages, raster group, cluster).  Tile K is 64; tile M is 128 per CTA.
-constexpr GemmConfig kConfigs[] = {
-    {256, 4, 8, 1},  {256, 4, 16, 1}, {256, 4, 4, 1},  {256, 4, 2, 1},
-    {128, 6, 8, 1},  {128, 6, 16, 1}, {128, 6, 4, 1},
-    {64, 8, 8, 1},   {64, 8, 16, 1},
-    {256, 6, 8, 2},  {256, 6, 4, 2},  {256, 6, 2, 2},  {256, 6, 16, 2},
-    {256, 7, 8, 2},  {256, 7, 16, 2}, {256, 7, 4, 2},
+// Every kernel instantiation in the library; the ring depths are the ones that fit 227 KB of
+// shared memory (bytes per stage = kps * 128 * (128 + bn) for one CTA, kps * 128 * (128 + bn / 2)
+// per CTA of a pair).
+constexpr GemmVariant kVariants[] = {
+    {1, 256, 4, 1}, {1, 256, 3, 1}, {1, 256, 2, 2},
+    {1, 128, 6, 1}, {1, 128, 4, 1}, {1, 128, 3, 2},
+    {1, 64, 8, 1},  {1, 64, 5, 1},  {1, 64, 4, 2},
+    {2, 256, 6, 1}, {2, 256, 7, 1}, {2, 256, 5, 1}, {2, 256, 3, 2},
+    {2, 128, 8, 1}, {2, 128, 6, 1}, {2, 128, 4, 2},
 };
-constexpr int kNumConfigs = sizeof(kConfigs) / sizeof(kConfigs[0]);
+constexpr int kRasters[] = {8, 16, 4, 2};        // M-tiles per sweep over N
+constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
+constexpr int kNumRasters = sizeof(kRasters) / sizeof(kRasters[0]);
+constexpr int kNumConfigs = kNumVariants * kNumRasters;   // config_id = variant * kNumRasters + raster index
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int KPS>
 hb_status launch_cfg(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p) {
-  using L = SmemLayout<BN, STAGES>;
-  auto kern = hb_gemm_bf16_kernel<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, KPS>;
+  static_assert(L::DYN_BYTES <= 227 * 1024, "ring does not fit shared memory");
+  auto kern = hb_gemm_bf16_kernel<BN, STAGES, KPS>;
   static bool attr_set[64] = {};
   if (!attr_set[ctx->device & 63]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -524,13 +558,13 @@ hb_status launch_cfg(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB
   return hb_check_cuda(ctx, cudaGetLastError(), "gemm launch");
 }
 
-template <int STAGES>
+template <int BN2, int STAGES, int KPS>
 hb_status launch_pair(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p) {
-  using L = SmemLayout2<STAGES>;
-  auto kern = hb_gemm_bf16_pair_kernel<STAGES>;
-  // The kernel is persistent: every cluster of the grid must be resident at once, so the
-  // grid is capped by what the occupancy query reports (not every SM has a pairable
-  // neighbour, so this is below sm_count / 2).
+  using L = SmemLayout2<BN2, STAGES, KPS>;
+  static_assert(L::DYN_BYTES <= 227 * 1024, "ring does not fit shared memory");
+  auto kern = hb_gemm_bf16_pair_kernel<BN2, STAGES, KPS>;
+  // The grid is capped by the number of clusters that can be resident at once (the occupancy
+  // query's answer: not every SM has a pairable neighbour, so this is below sm_count / 2).
   static int resident_pairs[64] = {};
   if (!resident_pairs[ctx->device & 63]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES);
@@ -551,7 +585,7 @@ hb_status launch_pair(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tm
     resident_pairs[ctx->device & 63] = n;
   }
   p.tiles_m = (p.M + 255) / 256;
-  p.tiles_n = (p.N + 255) / 256;
+  p.tiles_n = (p.N + BN2 - 1) / BN2;
   const int tiles = p.tiles_m * p.tiles_n;
   const int max_pairs = resident_pairs[ctx->device & 63];
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
@@ -569,89 +603,63 @@ bool hb_gemm_config_supports(int id, const hb_gemm_args& a) {
 }
 
 void hb_gemm_config_describe(int id, hb_tune_result* out) {
-  const GemmConfig& c = kConfigs[id];
+  const GemmVariant& v = kVariants[id / kNumRasters];
   out->config_id = id;
-  out->tile_m = BM;
-  out->tile_n = c.bn;
-  out->tile_k = BK;
-  out->stages = c.stages;
-  out->cluster = c.cluster;
-  if (c.cluster == 2) out->tile_m = 256;
-  out->raster_group = c.raster_group;
+  out->tile_m = v.cluster == 2 ? 256 : BM;
+  out->tile_n = v.bn;
+  out->tile_k = BK * v.kps;
+  out->stages = v.stages;
+  out->cluster = v.cluster;
+  out->raster_group = kRasters[id % kNumRasters];
   out->split_k = 1;
+}
+
+// The configuration with these properties, or -1 (the persisted cache names configurations by
+// their properties, so that it survives changes of this table).
+int hb_gemm_find_config(int cluster, int tile_n, int tile_k, int stages, int raster_group) {
+  for (int id = 0; id < kNumConfigs; ++id) {
+    const GemmVariant& v = kVariants[id / kNumRasters];
+    if (v.cluster == cluster && v.bn == tile_n && BK * v.kps == tile_k && v.stages == stages &&
+        kRasters[id % kNumRasters] == raster_group)
+      return id;
+  }
+  return -1;
 }
 
 hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id) {
   if (config_id < 0 || config_id >= kNumConfigs)
     return hb_fail(ctx, HB_ERR_INVALID, "matmul: config_id %d out of range [0,%d)", config_id,
                    kNumConfigs);
-  const GemmConfig cfg = kConfigs[config_id];
+  const GemmVariant cfg = kVariants[config_id / kNumRasters];
+  const int bn_cta = cfg.cluster == 2 ? cfg.bn / 2 : cfg.bn;     // B rows one CTA loads per k-block
+  // K-major operand: dims (K, rows), box (64, rows per CTA); MN-major: dims (rows, K), boxes of (64, 64)
   CUtensorMap tmA, tmB;
   hb_status st;
-  if (cfg.cluster == 2) {
-    // K-major operand: dims (K, rows), box (64, 128); MN-major: dims (rows, K), box (64, 64) twice
-    uint64_t dimsA[2] = {(uint64_t)(a.a_mn_major ? a.M : a.K), (uint64_t)(a.a_mn_major ? a.K : a.M)};
-    uint64_t dimsB[2] = {(uint64_t)(a.b_mn_major ? a.N : a.K), (uint64_t)(a.b_mn_major ? a.K : a.N)};
-    uint64_t strA[1] = {(uint64_t)a.lda * 2}, strB[1] = {(uint64_t)a.ldb * 2};
-    uint32_t boxA[2] = {64, a.a_mn_major ? 64u : 128u}, boxB[2] = {64, a.b_mn_major ? 64u : 128u};
-    if ((st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dimsA, strA, boxA,
-                                 CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
-    if ((st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dimsB, strB, boxB,
-                                 CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
-    GemmParams p;
-    p.C = static_cast<__nv_bfloat16*>(a.C);
-    p.R = static_cast<const __nv_bfloat16*>(a.residual);
-    p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
-    p.ldc = a.ldc; p.ldr = a.ldr;
-    p.raster_group = cfg.raster_group;
-    p.epilogue = a.epilogue;
-    p.a_mn = a.a_mn_major; p.b_mn = a.b_mn_major;
-    p.status = ctx->d_status;
-    return cfg.stages == 7 ? launch_pair<7>(ctx, tmA, tmB, p) : launch_pair<6>(ctx, tmA, tmB, p);
-  }
-  // A: K-major -> dims (K, M), box (64, 128); M-major -> dims (M, K), box (64, 64) x2.
-  if (!a.a_mn_major) {
-    uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.M};
-    uint64_t strides[1] = {(uint64_t)a.lda * 2};
-    uint32_t box[2] = {BK, BM};
-    st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
-  } else {
-    uint64_t dims[2] = {(uint64_t)a.M, (uint64_t)a.K};
-    uint64_t strides[1] = {(uint64_t)a.lda * 2};
-    uint32_t box[2] = {64, BK};
-    st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
-  }
-  if (st != HB_OK) return st;
-  if (!a.b_mn_major) {
-    uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.N};
-    uint64_t strides[1] = {(uint64_t)a.ldb * 2};
-    uint32_t box[2] = {BK, (uint32_t)cfg.bn};
-    st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
-  } else {
-    uint64_t dims[2] = {(uint64_t)a.N, (uint64_t)a.K};
-    uint64_t strides[1] = {(uint64_t)a.ldb * 2};
-    uint32_t box[2] = {64, BK};
-    st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_128B);
-  }
-  if (st != HB_OK) return st;
-
+  uint64_t dimsA[2] = {(uint64_t)(a.a_mn_major ? a.M : a.K), (uint64_t)(a.a_mn_major ? a.K : a.M)};
+  uint64_t dimsB[2] = {(uint64_t)(a.b_mn_major ? a.N : a.K), (uint64_t)(a.b_mn_major ? a.K : a.N)};
+  uint64_t strA[1] = {(uint64_t)a.lda * 2}, strB[1] = {(uint64_t)a.ldb * 2};
+  uint32_t boxA[2] = {64, a.a_mn_major ? 64u : 128u}, boxB[2] = {64, a.b_mn_major ? 64u : (uint32_t)bn_cta};
+  if ((st = hb_make_tensor_map(ctx, &tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.A, dimsA, strA, boxA,
+                               CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
+  if ((st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dimsB, strB, boxB,
+                               CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
   GemmParams p;
   p.C = static_cast<__nv_bfloat16*>(a.C);
   p.R = static_cast<const __nv_bfloat16*>(a.residual);
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.ldc = a.ldc; p.ldr = a.ldr;
-  p.raster_group = cfg.raster_group;
+  p.raster_group = kRasters[config_id % kNumRasters];
   p.epilogue = a.epilogue;
   p.a_mn = a.a_mn_major; p.b_mn = a.b_mn_major;
   p.status = ctx->d_status;
-  switch (cfg.bn) {
-    case 256: return launch_cfg<256, 4>(ctx, tmA, tmB, p);
-    case 128: return launch_cfg<128, 6>(ctx, tmA, tmB, p);
-    case 64:  return launch_cfg<64, 8>(ctx, tmA, tmB, p);
-  }
-  return hb_fail(ctx, HB_ERR_INVALID, "matmul: bad config");
+#define HB_CASE1(BN, ST, KP) if (cfg.cluster == 1 && cfg.bn == BN && cfg.stages == ST && cfg.kps == KP) return launch_cfg<BN, ST, KP>(ctx, tmA, tmB, p)
+#define HB_CASE2(BN, ST, KP) if (cfg.cluster == 2 && cfg.bn == BN && cfg.stages == ST && cfg.kps == KP) return launch_pair<BN, ST, KP>(ctx, tmA, tmB, p)
+  HB_CASE1(256, 4, 1); HB_CASE1(256, 3, 1); HB_CASE1(256, 2, 2);
+  HB_CASE1(128, 6, 1); HB_CASE1(128, 4, 1); HB_CASE1(128, 3, 2);
+  HB_CASE1(64, 8, 1);  HB_CASE1(64, 5, 1);  HB_CASE1(64, 4, 2);
+  HB_CASE2(256, 6, 1); HB_CASE2(256, 7, 1); HB_CASE2(256, 5, 1); HB_CASE2(256, 3, 2);
+  HB_CASE2(128, 8, 1); HB_CASE2(128, 6, 1); HB_CASE2(128, 4, 2);
+#undef HB_CASE1
+#undef HB_CASE2
+  return hb_fail(ctx, HB_ERR_INVALID, "matmul: configuration %d has no kernel", config_id);
 }

@@ -252,7 +252,9 @@ hb_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_cons
   }
 }
 
-int skinny_kps() {
+// k-blocks per ring stage: the given value if valid, else HB_SKINNY_KPS, else 2.
+int skinny_kps(int want) {
+  if (want == 1 || want == 2 || want == 4) return want;
   int k = 2;
   if (const char* e = getenv("HB_SKINNY_KPS")) { const int v = atoi(e); if (v == 1 || v == 2 || v == 4) k = v; }
   return k;
@@ -275,15 +277,18 @@ bool hb_gemm_skinny_applicable(const hb_gemm_args& a) {
 
 // Chooses the grid and reports the scratch the launch needs: `grid` persistent CTAs, at
 // most `max_seg` ranges per tile, `partial_floats` floats of partials, `tiles` tickets.
-void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int* grid, int* max_seg,
+// `grid_cap` (<= 0: one CTA per SM, or HB_SKINNY_CTAS) and `kps` (<= 0: default) are the two
+// axes the autotuner searches.
+void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int grid_cap, int kps_in, int* grid, int* max_seg,
                          size_t* partial_floats, int* tiles) {
   const int t = (int)((N + BN_ROWS - 1) / BN_ROWS);
-  const int kps = skinny_kps();
+  const int kps = skinny_kps(kps_in);
   const int num_kb = (int)((K + BK * kps - 1) / (BK * kps));      // k-groups per tile
   const int mpad = (int)((M + 15) / 16) * 16;
   const int64_t units = (int64_t)t * num_kb;
   int g = sm_count;
-  if (const char* e = getenv("HB_SKINNY_CTAS")) { const int v = atoi(e); if (v >= 1) g = v; }
+  if (grid_cap >= 1) g = grid_cap < sm_count ? grid_cap : sm_count;
+  else if (const char* e = getenv("HB_SKINNY_CTAS")) { const int v = atoi(e); if (v >= 1) g = v; }
   if (units / 4 < g) g = (int)(units / 4 > 0 ? units / 4 : 1);     // at least 4 k-groups per CTA
   const int64_t per = units / g;                                     // shortest range
   int ms = (int)((num_kb + per - 1) / per) + 1;
@@ -295,7 +300,7 @@ void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int* gri
 }
 
 hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_gemm_args& a, float* partial, int* tickets,
-                                    int grid, int max_seg, int tiles, int32_t* status) {
+                                    int grid, int max_seg, int tiles, int kps, int32_t* status) {
   CUtensorMap tmA, tmB;
   const int mpad = (int)((a.M + 15) / 16) * 16;
   {
@@ -322,7 +327,7 @@ hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_g
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
   p.ldc = a.ldc;
   p.mpad = mpad;
-  p.kps = skinny_kps();
+  p.kps = skinny_kps(kps);
   p.stages = skinny_stages(mpad, p.kps);
   p.a_bytes = mpad * 128;
   p.num_kb = (int)((a.K + BK * p.kps - 1) / (BK * p.kps));
@@ -347,18 +352,25 @@ hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_g
   return hb_check_cuda(ctx, cudaGetLastError(), "skinny gemm launch");
 }
 
-hb_status hb_launch_gemm_skinny(hb_ctx* ctx, const hb_gemm_args& a) {
+hb_status hb_launch_gemm_skinny_cfg(hb_ctx* ctx, const hb_gemm_args& a, int grid_cap, int kps) {
   int grid, max_seg, tiles;
   size_t floats;
-  hb_gemm_skinny_plan(ctx->sm_count, a.M, a.N, a.K, &grid, &max_seg, &floats, &tiles);
+  hb_gemm_skinny_plan(ctx->sm_count, a.M, a.N, a.K, grid_cap, kps, &grid, &max_seg, &floats, &tiles);
   if (tiles > HB_MAX_SPLITK_TILES) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "matmul: N too large for the split-K path");
   void* ws = nullptr;
   hb_status st = hb_get_scratch(ctx, HB_SCRATCH_WORKSPACE, floats * sizeof(float), &ws);
   if (st != HB_OK) return st;
-  st = hb_launch_gemm_skinny_raw(ctx, ctx->stream, a, static_cast<float*>(ws), ctx->d_tickets, grid, max_seg, tiles,
+  st = hb_launch_gemm_skinny_raw(ctx, ctx->stream, a, static_cast<float*>(ws), ctx->d_tickets, grid, max_seg, tiles, kps,
                                  ctx->d_status);
   if (st == HB_OK) ctx->launches++;
   return st;
+}
+
+// The autotune cache's (grid, k-blocks per stage) for this shape when it has one.
+hb_status hb_launch_gemm_skinny(hb_ctx* ctx, const hb_gemm_args& a) {
+  int grid_cap = 0, kps = 0;
+  if (!hb_skinny_cached_choice(ctx, a, &grid_cap, &kps)) { grid_cap = 0; kps = 0; }
+  return hb_launch_gemm_skinny_cfg(ctx, a, grid_cap, kps);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -459,7 +471,7 @@ extern "C" hb_status hb_matmul_skinny_static(const void* A, const void* B, void*
   if (st != HB_OK) return st;
   int grid, max_seg, tiles;
   size_t floats;
-  hb_gemm_skinny_plan(d->sm_count, M, N, K, &grid, &max_seg, &floats, &tiles);
+  hb_gemm_skinny_plan(d->sm_count, M, N, K, 0, 0, &grid, &max_seg, &floats, &tiles);
   if (tiles > HB_STATIC_MAX_TILES || floats > HB_STATIC_MAX_PARTIAL_FLOATS) {
     char detail[128];
     snprintf(detail, sizeof(detail), "needs %zu partial floats over %d tiles; the static scratch holds %zu floats and %d tiles",
@@ -474,7 +486,7 @@ extern "C" hb_status hb_matmul_skinny_static(const void* A, const void* B, void*
   a.A = A; a.B = B; a.C = C;
   a.M = M; a.N = N; a.K = K;
   a.lda = K; a.ldb = K; a.ldc = N;
-  st = hb_launch_gemm_skinny_raw(nullptr, stream, a, d->partial, d->tickets, grid, max_seg, tiles, d->status);
+  st = hb_launch_gemm_skinny_raw(nullptr, stream, a, d->partial, d->tickets, grid, max_seg, tiles, 0, d->status);
   if (st != HB_OK) return static_fail(st, "skinny_static: launch failed (descriptor encoding or kernel launch)");
   return HB_OK;
 }

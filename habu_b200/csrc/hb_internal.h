@@ -23,9 +23,11 @@ enum { HB_SCRATCH_WORKSPACE = 0, HB_SCRATCH_STAGING = 1, HB_SCRATCH_TUNE = 2, HB
 constexpr int HB_MAX_SPLITK_TILES = 4096;
 
 struct hb_tune_entry {
-  int32_t config_id;
+  int32_t config_id;   // matmul: index in the configuration table; attention: 0 one unit per CTA, 1 persistent
   float ms;
+  int32_t p0, p1;      // stream-K matmul: grid, k-blocks per ring stage
 };
+enum { HB_OP_SKINNY = 2 };   // cache lines of the stream-K kernel (reached through HB_OP_MATMUL with M <= 64)
 
 // One encoded TMA descriptor and the arguments it was encoded from (see hb_make_tensor_map).
 struct hb_tmap_entry {
@@ -48,6 +50,7 @@ struct hb_p2p_state {
 struct hb_ctx {
   int device = 0;
   int sm_count = 0;
+  std::string gpu_name;               // device name with blanks replaced by '_' (part of the autotune key)
   cudaStream_t stream = nullptr;      // stream in use
   cudaStream_t own_stream = nullptr;  // created by the context
   cudaStream_t side_stream = nullptr; // second stream for executor nodes that overlap (collectives)
@@ -99,7 +102,8 @@ hb_status hb_make_tensor_map(hb_ctx* ctx, CUtensorMap* out, CUtensorMapDataType 
                              const void* base, const uint64_t* dims, const uint64_t* strides_bytes,
                              const uint32_t* box, CUtensorMapSwizzle swizzle);
 
-std::string hb_tune_key(const hb_op_desc& d, int sm_count, int world);
+std::string hb_tune_key(const hb_op_desc& d, int sm_count, const std::string& gpu);
+int hb_attention_cached_choice(hb_ctx* ctx, int64_t batch, int64_t seq, int64_t hq, int64_t hkv, int causal);
 
 // Kernel launchers (each validates nothing: callers validated already).
 struct hb_gemm_args {
@@ -119,7 +123,11 @@ int hb_gemm_pick_config(hb_ctx* ctx, const hb_gemm_args& a);
 // Split-K path for M <= 64 (decode-shaped) products.
 bool hb_gemm_skinny_applicable(const hb_gemm_args& a);
 hb_status hb_launch_gemm_skinny(hb_ctx* ctx, const hb_gemm_args& a);
-void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int* grid, int* max_seg,
+// Same with the grid (persistent CTAs) and the k-blocks per ring stage given (the autotuner's axes).
+hb_status hb_launch_gemm_skinny_cfg(hb_ctx* ctx, const hb_gemm_args& a, int grid_cap, int kps);
+bool hb_skinny_cached_choice(hb_ctx* ctx, const hb_gemm_args& a, int* grid, int* kps);
+// grid_cap <= 0: one CTA per SM; kps <= 0: the default (2).
+void hb_gemm_skinny_plan(int sm_count, int64_t M, int64_t N, int64_t K, int grid_cap, int kps, int* grid, int* max_seg,
                          size_t* partial_floats, int* tiles);
 hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_gemm_args& a, float* partial, int* tickets,
-                                    int grid, int max_seg, int tiles, int32_t* status);
+                                    int grid, int max_seg, int tiles, int kps, int32_t* status);

@@ -34,6 +34,9 @@ extern "C" hb_status hb_ctx_create(int32_t device, hb_ctx** out) {
   hb_ctx* ctx = new hb_ctx();
   ctx->device = device;
   ctx->sm_count = prop.multiProcessorCount;
+  ctx->gpu_name = prop.name;
+  for (char& c : ctx->gpu_name)
+    if (c == ' ' || c == '\t') c = '_';
   if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&ctx->d_status, 16 * sizeof(int32_t)) != cudaSuccess ||     // 4 status words, 4 spare, 8 work counters
       cudaMemset(ctx->d_status, 0, 16 * sizeof(int32_t)) != cudaSuccess ||

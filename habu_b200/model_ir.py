@@ -361,6 +361,14 @@ class Context:
         self._check(_lib.hb_autotune(self._h, C.byref(d), HB_TUNE_SEARCH if search else HB_TUNE_CACHED, C.byref(r)))
         return r
 
+    def autotune_attention(self, batch: int, seq: int, n_q_heads: int, n_kv_heads: int, causal: bool = True,
+                           search: bool = True) -> _capi.hb_tune_result:
+        """Attention node: one work unit per CTA (config 0) against the persistent work queue (1)."""
+        d = _capi.hb_op_desc(_capi.HB_OP_ATTENTION, HB_BF16, batch, seq, 128, int(causal), (n_q_heads << 16) | n_kv_heads)
+        r = _capi.hb_tune_result()
+        self._check(_lib.hb_autotune(self._h, C.byref(d), HB_TUNE_SEARCH if search else HB_TUNE_CACHED, C.byref(r)))
+        return r
+
     def tune_cache_save(self, path: str):
         self._check(_lib.hb_tune_cache_save(self._h, path.encode()))
 

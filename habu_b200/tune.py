@@ -3,9 +3,9 @@
     python -m habu_b200.tune                 # the benchmark configurations' shapes
     python -m habu_b200.tune 4096x4096x4096  # M x N x K [x layout [x epilogue]]
 
-The cache (``habu_b200/tune_cache.txt``, one text line per shape and SM count) is loaded
-by every :class:`habu_b200.Context` at creation; shapes without an entry use the
-heuristic in the library.
+The cache (``habu_b200/tune_cache.txt``, one text line per operator, shape, SM count and GPU
+name, the choice written by its properties) is loaded by every :class:`habu_b200.Context` at
+creation; shapes without an entry use the heuristic in the library.
 """
 from __future__ import annotations
 
@@ -31,6 +31,16 @@ def default_shapes():
     return out
 
 
+# Decode-shaped products (M = 16 new tokens) of the same block, and the attention shapes of the
+# benchmark and of the decoder at TP 1/2/4/8: (batch, seq, q heads, kv heads, causal).
+def default_skinny_shapes():
+    return [(16, 8192, 8192), (16, 6144, 4096), (16, 4096, 4096), (16, 28672, 4096), (16, 4096, 14336)]
+
+
+def default_attention_shapes():
+    return [(8, 4096, 32, 8, True)] + [(4, 2048, 32 // tp, 8 // tp, True) for tp in (1, 2, 4, 8)]
+
+
 def main(argv):
     import habu_b200 as hb
     ctx = hb.Context(0, load_tune_cache=False)
@@ -40,8 +50,18 @@ def main(argv):
     for s in shapes:
         m, n, k, layout, epi = s[:5]
         r = ctx.autotune(m, n, k, layout, epi, search=True)
-        print(f"{m}x{n}x{k} layout {layout} epilogue {epi}: config {r.config_id} (tile {r.tile_m}x{r.tile_n}x{r.tile_k}, "
-              f"{r.stages} stages, raster {r.raster_group}) {r.ms * 1e3:.1f} us {r.tflops:.0f} TFLOP/s", flush=True)
+        print(f"{m}x{n}x{k} layout {layout} epilogue {epi}: config {r.config_id} (cluster {r.cluster}, tile "
+              f"{r.tile_m}x{r.tile_n}x{r.tile_k}, {r.stages} stages, raster {r.raster_group}) {r.ms * 1e3:.1f} us "
+              f"{r.tflops:.0f} TFLOP/s", flush=True)
+    if not argv:
+        for m, n, k in default_skinny_shapes():
+            r = ctx.autotune(m, n, k, search=True)
+            print(f"{m}x{n}x{k} stream-K: grid {r.split_k}, {r.tile_k // 64} k-blocks per stage, {r.ms * 1e3:.1f} us "
+                  f"{2.0 * (m * k + n * k + m * n) / (r.ms * 1e-3) / 1e9:.0f} GB/s", flush=True)
+        for b, s_, hq, hkv, causal in default_attention_shapes():
+            r = ctx.autotune_attention(b, s_, hq, hkv, causal, search=True)
+            print(f"attention batch {b} seq {s_} heads {hq}/{hkv}: {'persistent' if r.config_id else 'one unit per CTA'} "
+                  f"{r.ms * 1e3:.1f} us {r.tflops:.0f} TFLOP/s", flush=True)
     ctx.tune_cache_save(CACHE)
     print(f"saved {CACHE}")
 

@@ -324,21 +324,30 @@ hb_status hb_graph_describe(hb_graph* g, char* buf, size_t len);
 hb_status hb_graph_tensor_ptr(hb_graph* g, int32_t id, void** ptr);
 
 /* ---- autotune entry point ----------------------------------------------------------
- * Searches tile shape / cluster shape / stage count / raster order for one problem
- * shape by timing each candidate on the device, records the winner in the context's
- * cache, and can persist the cache as text.  No reference counterpart. */
+ * Searches the configurations of one operator for one problem shape by timing each
+ * candidate on the device, records the winner in the context's cache, and can persist the
+ * cache as text.  No reference counterpart.
+ *   matmul (M > 64)   tile N (64 / 128 / 256), cluster shape (one CTA per 128-row tile or a CTA
+ *                     pair per 256-row tile), ring depth, K-block width (64 or 128 per ring
+ *                     stage) and raster order, each varied on its own;
+ *   matmul (M <= 64)  the stream-K kernel: persistent grid and k-blocks per ring stage;
+ *   attention         one work unit per CTA or the persistent work queue.
+ * The text cache writes a choice by its properties and keys it by operator, shape, layout,
+ * epilogue, SM count and GPU name (hb_tune_cache_save / _load; version-1 files are read). */
 enum { HB_OP_MATMUL = 0, HB_OP_ATTENTION = 1 };
 enum { HB_TUNE_CACHED = 0, HB_TUNE_SEARCH = 1 };
 typedef struct hb_op_desc {
   int32_t op;              /* HB_OP_* */
   int32_t dtype;
-  int64_t m, n, k;         /* matmul: M,N,K; attention: batch*heads, seq, head_dim */
-  int32_t layout;          /* matmul: bit0 A is M-major, bit1 B is N-major */
-  int32_t epilogue;
+  int64_t m, n, k;         /* matmul: M,N,K; attention: batch, seq, head_dim (128) */
+  int32_t layout;          /* matmul: bit0 A is M-major, bit1 B is N-major; attention: 1 = causal */
+  int32_t epilogue;        /* matmul: HB_EPI_*; attention: n_q_heads << 16 | n_kv_heads */
 } hb_op_desc;
 typedef struct hb_tune_result {
-  int32_t config_id;
-  int32_t tile_m, tile_n, tile_k, stages, cluster, raster_group, split_k;
+  int32_t config_id;       /* matmul: index for hb_matmul_opts.config_id (-1: stream-K kernel);
+                              attention: 0 one unit per CTA, 1 persistent (hb_attn_opts.config_id) */
+  int32_t tile_m, tile_n, tile_k, stages, cluster, raster_group;
+  int32_t split_k;         /* stream-K kernel: persistent grid (K ranges in flight); else 1 */
   float ms;
   float tflops;
 } hb_tune_result;
