@@ -293,23 +293,65 @@ class DecoderWorkload:
             full = decoder.make_layer(cfg, i)
             layers.append({k: oracle.to_bf16_bits(v) for k, v in shard_layer(full, cfg, world, rank).items()})
             del full
-        # micro-batches whose allreduce overlaps the next chunk's GEMMs (only useful with peers)
-        self.chunks = int(os.environ.get("HB_DECODER_CHUNKS", "1"))
-        # fused reduce-scatter + residual + RMSNorm + all-gather nodes instead of allreduce + replicated norms
-        self.fused = os.environ.get("HB_DECODER_FUSED", "1") == "1" and world > 1
-        self.dg = DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO, self.chunks, fused=self.fused)
-        _, sym = self.dg.plan()
+        # How the collectives overlap the products around them is a schedule choice that depends on
+        # the rank count and the fabric: the candidates (habu_b200.tp.candidate_schedules; all
+        # compute the same values) are timed here, outside the timed region, and the fastest one
+        # is what the step runs.  HB_DECODER_SCHEDULE=i pins candidate i; HB_DECODER_FUSED=0 and
+        # HB_DECODER_CHUNKS=n select the unfused allreduce graph as before.
+        from habu_b200.tp import candidate_schedules, pick_schedule
+        if os.environ.get("HB_DECODER_FUSED", "1") != "1" or "HB_DECODER_CHUNKS" in os.environ:
+            cands = [dict(chunks=int(os.environ.get("HB_DECODER_CHUNKS", "1")),
+                          fused=os.environ.get("HB_DECODER_FUSED", "1") == "1")]
+        else:
+            cands = candidate_schedules(world)
+            if "HB_DECODER_SCHEDULE" in os.environ:
+                cands = [cands[int(os.environ["HB_DECODER_SCHEDULE"])]]
+        graphs = []
+        for c in cands:
+            graphs.append(DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO, share=graphs[0] if graphs else None, **c))
+        sym = max(g.plan()[1] for g in graphs)
         if world > 1:
             ids = [ctx.comm_unique_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             ctx.comm_init_rank(world, rank, ids[0])
             _, self.comm = attach_symmetric(ctx, rank, world, dist, sym)
-            self.dg.plan()
+            for g in graphs:
+                g.plan()
         x0 = oracle.to_bf16_bits(decoder.make_input(cfg))
         self.hX = pinned(x0)
         self.hO = pinned(np.empty_like(x0))
-        self._copy(ctx, self.dg.x0.ptr, self.hX, up=True)
+        self._copy(ctx, graphs[0].x0.ptr, self.hX, up=True)
         ctx.sync()
+        self.schedule_search = None
+        if len(graphs) > 1:
+            import torch
+
+            stream = self.torch_stream          # the stream the context launches on (set by main)
+
+            def measure(run, n=8):
+                for _ in range(2):
+                    run()
+                ctx.sync()
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(n):
+                    run()
+                e1.record(stream)
+                ctx.sync()
+                torch.cuda.synchronize()
+                t = torch.tensor([e0.elapsed_time(e1) / n], device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                return float(t.item())
+            best, times = pick_schedule(graphs, measure)
+            self.schedule_search = [{**g.schedule, "ms": round(t, 4)} for g, t in zip(graphs, times)]
+        else:
+            best = 0
+        self.dg = graphs[best]
+        for i, g in enumerate(graphs):
+            if i != best:
+                g.graph.close()
         self.h2d, self.d2h = x0.nbytes, x0.nbytes
         self.world = world
 
@@ -739,6 +781,7 @@ def main():
         ctx = hb.Context(local_rank)
         ctx.set_stream(stream.cuda_stream)
         wl = WORKLOADS[name]()
+        wl.torch_stream = stream
         sharded = getattr(wl, "collective", False)        # the step has a real exchange between ranks
         strong = getattr(wl, "scaling", "weak") == "strong"
         if sharded:
@@ -802,6 +845,10 @@ def main():
             roof["note"] = "whole-step figure: algorithmic flop of the block / (n_gpus x step time), all kernels and collectives included"
         if hasattr(wl, "comm"):
             roof["collective"] = wl.comm
+        if getattr(wl, "dg", None) is not None and hasattr(wl.dg, "schedule"):
+            roof["schedule"] = wl.dg.schedule
+            if getattr(wl, "schedule_search", None):
+                roof["schedule_search"] = wl.schedule_search
         res = {"metric": wl.metric, "value": value, "unit": wl.unit, "ms_per_step": ms_per_step, "steps": steps,
                "scaling": getattr(wl, "scaling", "weak"), "workload": wl.desc, "l2": wl.flush_note, "roofline": roof,
                "gpu_launches": launches, "clocks": clocks}

@@ -79,6 +79,7 @@ def load() -> C.CDLL:
         "hb_download": [vp, vp, vp, C.c_size_t],
         "hb_sync": [vp],
         "hb_matmul": [vp, T, T, T, C.POINTER(hb_matmul_opts)],
+        "hb_matmul_gathered": [vp, T, T, T, C.POINTER(hb_matmul_opts)],
         "hb_matmul_host": [vp, vp, vp, vp, i64, i64, i64, i32],
         "hb_matmul_skinny_static": [vp, vp, vp, i64, i64, i64, i32, vp],
         "hb_static_status": [i32, C.POINTER(i32)],
@@ -105,6 +106,7 @@ def load() -> C.CDLL:
         "hb_p2p_attach_external": [vp, i32, i32, C.POINTER(vp), vp, C.c_size_t],
         "hb_all_reduce": [vp, vp, i64, i32, i32],
         "hb_comm_set_wait_limit": [vp, C.c_uint32],
+        "hb_comm_configure": [vp, i32, i32],
         "hb_all_reduce_async": [vp, vp, i64, i32, i32],
         "hb_side_join": [vp],
         "hb_all_reduce_norm": [vp, vp, vp, vp, vp, vp, i64, i64, f32, i32, i32],

@@ -66,7 +66,14 @@ NcclApi* nccl_api() {
 constexpr int AR_MAX_WORLD = 8;
 constexpr int AR_MAX_CTAS = 296;                       // 2 per SM on a 148-SM part
 constexpr int AR_THREADS = 256;
-constexpr size_t AR_FLAG_BYTES = 2 * AR_MAX_CTAS * AR_MAX_WORLD * sizeof(uint32_t);
+constexpr size_t AR_HANDSHAKE_BYTES = 2 * AR_MAX_CTAS * AR_MAX_WORLD * sizeof(uint32_t);
+// After the per-CTA handshake words: one "rows ready" word per block of gathered rows (written by
+// the block's owner into every rank's copy, read by the matmul that consumes the rows) and one
+// arrival counter per block (local use: the rows of a block are normalised by different warps).
+constexpr int AR_MAX_READY = 512;
+constexpr size_t AR_READY_OFF = AR_HANDSHAKE_BYTES;
+constexpr size_t AR_COUNT_OFF = AR_READY_OFF + AR_MAX_READY * sizeof(uint32_t);
+constexpr size_t AR_FLAG_BYTES = AR_COUNT_OFF + AR_MAX_READY * sizeof(uint32_t);
 
 struct ArParams {
   void* peers[AR_MAX_WORLD];      // base of every rank's symmetric buffer (data first)
@@ -374,6 +381,16 @@ extern "C" hb_status hb_p2p_attach(hb_ctx* ctx, int32_t world, int32_t rank, con
 }
 
 extern "C" size_t hb_p2p_flag_bytes(void) { return AR_FLAG_BYTES; }
+size_t hb_p2p_ready_offset() { return AR_READY_OFF; }
+
+extern "C" hb_status hb_comm_configure(hb_ctx* ctx, int32_t fused_form, int32_t fused_ctas) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (fused_form < 0 || fused_form > 2 || fused_ctas < 0)
+    return hb_fail(ctx, HB_ERR_INVALID, "comm: fused_form must be 0 (automatic), 1 (CTA per row) or 2 (warp per row)");
+  ctx->p2p.fused_form = fused_form;
+  ctx->p2p.fused_ctas = fused_ctas;
+  return HB_OK;
+}
 
 extern "C" hb_status hb_comm_set_wait_limit(hb_ctx* ctx, uint32_t polls) {
   if (!ctx) return HB_ERR_INVALID;
@@ -513,6 +530,7 @@ struct ArnParams {
   float inv_cols, eps;
   int mode;
   int stagger;                 // rows kernel: pace warps 4..7 behind warps 0..3 (in-switch form)
+  int ready_rows;              // rows per "rows ready" word (0: none are published)
 };
 
 template <bool NVLS, int WORLD>
@@ -641,14 +659,17 @@ hb_allreduce_norm_kernel(const ArnParams p) {
 // rmsnorm_kernel (lane l of virtual warp w sums vectors c = 32 (w + 8 k) + l, k = 0..3; then
 // the shuffle tree; then the eight warp sums in order), so the results are the same bits.
 constexpr int ARW_VEC = 16;    // 16-byte vectors per lane: cols <= 32 * 16 * 8 = 4096
+constexpr int ARW_ROUNDS = 64; // most rounds (rows per warp) when ready words are published
 
 template <bool NVLS, int WORLD>
-__global__ void __launch_bounds__(AR_THREADS, 1)
+__global__ void __launch_bounds__(AR_THREADS, 2)
 hb_allreduce_norm_rows_kernel(const ArnParams p) {
   // Pacing between the two halves of the CTA (see `stagger` below).
   __shared__ volatile int loaded[AR_THREADS / 64];
+  __shared__ int round_rows[ARW_ROUNDS];       // rows of this CTA done per round (ready words)
   const int cta = blockIdx.x;
   if (threadIdx.x < AR_THREADS / 64) loaded[threadIdx.x] = 0;
+  if (threadIdx.x < ARW_ROUNDS) round_rows[threadIdx.x] = 0;
   if (!ar_barrier(p.ar, 0, cta)) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int per = p.rows / p.ar.world;
@@ -680,7 +701,7 @@ hb_allreduce_norm_rows_kernel(const ArnParams p) {
         if (c < p.cols8) s[k] = multimem_ld_reduce_bf16(p.mc + p.ar.data_off + (base + c) * 16);
       }
     } else {
-#pragma unroll 2
+#pragma unroll
       for (int k = 0; k < ARW_VEC; ++k) {
         const int c = lane + 32 * k;
         if (c < p.cols8) {
@@ -762,6 +783,35 @@ hb_allreduce_norm_rows_kernel(const ArnParams p) {
         }
       }
     }
+    if (p.ready_rows) {
+      // "Rows ready" words: a matmul that consumes the gathered rows waits for the word of a
+      // block of rows instead of for the end of this kernel.  A system-scope fence is costly
+      // (it waits for the SM's stores in flight), so there is one per CTA and round, not one per
+      // row: the eight rows a CTA handles in a round lie in one block; each warp counts its row
+      // in shared memory, and the warp that completes the CTA's share fences once, adds the
+      // share to the block's counter, and, if that completes the block, writes the word into
+      // every rank's copy.  Only that one warp waits; the others go on to their next rows.
+      __syncwarp();
+      if (lane == 0) {
+        const int first = row0 + round * nwarps + cta * (AR_THREADS / 32);   // the CTA's first row of this round
+        const int share = min(AR_THREADS / 32, row0 + per - first);
+        __threadfence_block();
+        if (atomicAdd(&round_rows[round & (ARW_ROUNDS - 1)], 1) == share - 1) {
+          round_rows[round & (ARW_ROUNDS - 1)] = 0;
+          __threadfence_system();                     // the CTA's rows of this round, before the count
+          const int blk = first / p.ready_rows;
+          char* mine = static_cast<char*>(p.ar.peers[p.ar.rank]) + p.ar.flag_off;
+          int* count = reinterpret_cast<int*>(mine + AR_COUNT_OFF) + blk;
+          if (atomicAdd(count, share) == p.ready_rows - share) {
+            *count = 0;                               // zero again for the next launch
+            __threadfence_system();                   // the other CTAs' rows, before the word
+            for (int r = 0; r < p.ar.world; ++r)
+              st_release_sys(reinterpret_cast<uint32_t*>(static_cast<char*>(p.ar.peers[r]) + p.ar.flag_off + AR_READY_OFF) + blk,
+                             p.ar.epoch);
+          }
+        }
+      }
+    }
   }
   if (p.stagger && !follower && lane == 0) loaded[pair_slot] = 1 << 30;   // no more rounds: followers run free
   ar_barrier(p.ar, 1, cta);
@@ -773,23 +823,26 @@ hb_allreduce_norm_rows_kernel(const ArnParams p) {
 // kernels ask for the largest shared-memory carve-out too (HB_AR_CARVEOUT=0 leaves the
 // driver's choice).
 template <typename K>
-void prefer_max_shared(K kernel) {
-  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+void set_carveout(K kernel, int value) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, value);
 }
 void comm_kernel_setup(hb_ctx* ctx) {
-  static bool done[64] = {};
-  if (done[ctx->device & 63]) return;
-  done[ctx->device & 63] = true;
+  static int applied[64];
+  static bool init = false;
+  if (!init) { for (int& a : applied) a = -2; init = true; }
+  int want = cudaSharedmemCarveoutMaxShared;
   if (const char* e = getenv("HB_AR_CARVEOUT"))
-    if (atoi(e) == 0) return;
-  prefer_max_shared(hb_allreduce_p2p_kernel<float, 2>); prefer_max_shared(hb_allreduce_p2p_kernel<float, 4>);
-  prefer_max_shared(hb_allreduce_p2p_kernel<float, 8>); prefer_max_shared(hb_allreduce_p2p_kernel<__nv_bfloat16, 2>);
-  prefer_max_shared(hb_allreduce_p2p_kernel<__nv_bfloat16, 4>); prefer_max_shared(hb_allreduce_p2p_kernel<__nv_bfloat16, 8>);
-  prefer_max_shared(hb_allreduce_nvls_kernel<float>); prefer_max_shared(hb_allreduce_nvls_kernel<__nv_bfloat16>);
-  prefer_max_shared(hb_allreduce_norm_kernel<true, 1>); prefer_max_shared(hb_allreduce_norm_kernel<false, 2>);
-  prefer_max_shared(hb_allreduce_norm_kernel<false, 4>); prefer_max_shared(hb_allreduce_norm_kernel<false, 8>);
-  prefer_max_shared(hb_allreduce_norm_rows_kernel<true, 1>); prefer_max_shared(hb_allreduce_norm_rows_kernel<false, 2>);
-  prefer_max_shared(hb_allreduce_norm_rows_kernel<false, 4>); prefer_max_shared(hb_allreduce_norm_rows_kernel<false, 8>);
+    if (atoi(e) == 0) want = cudaSharedmemCarveoutDefault;
+  if (applied[ctx->device & 63] == want) return;
+  applied[ctx->device & 63] = want;
+  set_carveout(hb_allreduce_p2p_kernel<float, 2>, want); set_carveout(hb_allreduce_p2p_kernel<float, 4>, want);
+  set_carveout(hb_allreduce_p2p_kernel<float, 8>, want); set_carveout(hb_allreduce_p2p_kernel<__nv_bfloat16, 2>, want);
+  set_carveout(hb_allreduce_p2p_kernel<__nv_bfloat16, 4>, want); set_carveout(hb_allreduce_p2p_kernel<__nv_bfloat16, 8>, want);
+  set_carveout(hb_allreduce_nvls_kernel<float>, want); set_carveout(hb_allreduce_nvls_kernel<__nv_bfloat16>, want);
+  set_carveout(hb_allreduce_norm_kernel<true, 1>, want); set_carveout(hb_allreduce_norm_kernel<false, 2>, want);
+  set_carveout(hb_allreduce_norm_kernel<false, 4>, want); set_carveout(hb_allreduce_norm_kernel<false, 8>, want);
+  set_carveout(hb_allreduce_norm_rows_kernel<true, 1>, want); set_carveout(hb_allreduce_norm_rows_kernel<false, 2>, want);
+  set_carveout(hb_allreduce_norm_rows_kernel<false, 4>, want); set_carveout(hb_allreduce_norm_rows_kernel<false, 8>, want);
   cudaGetLastError();
 }
 
@@ -801,6 +854,8 @@ extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const 
   if (!ctx) return HB_ERR_INVALID;
   if (!partial || !residual_in || !residual_out || !out || (mode == 0 && !gain))
     return hb_fail(ctx, HB_ERR_INVALID, "all_reduce_norm: null pointer");
+  const bool publish = (mode & 2) != 0;      // publish "rows ready" words for hb_matmul_gathered
+  mode &= ~2;
   if (mode != 0 && mode != 1) return hb_fail(ctx, HB_ERR_INVALID, "all_reduce_norm: unknown mode %d", mode);
   hb_p2p_state& s = ctx->p2p;
   if (s.world < 2) return hb_fail(ctx, HB_ERR_NOT_FOUND, "all_reduce_norm: no peer buffers attached");
@@ -838,12 +893,24 @@ extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const 
   p.eps = eps;
   p.mode = mode;
   comm_kernel_setup(ctx);
-  bool by_rows = cols <= 32 * ARW_VEC * 8;            // warp-per-row form
-  if (const char* e = getenv("HB_ARN_ROWS")) by_rows = by_rows && atoi(e) != 0;
+  // Two forms of the kernel.  One CTA per row (two rows in flight per CTA, up to two CTAs per
+  // SM) is the faster one when the collective has the GPU to itself: measured 194 us against
+  // 233 us for a 64 MiB exchange over 8 GPUs.  One warp per row needs few CTAs and at most 128
+  // registers, which is what lets it run beside a GEMM on the same SMs: the form for
+  // collectives that overlap compute.  hb_comm_configure chooses; the default is the CTA-per-row
+  // form on the context's own stream and the warp-per-row form on the side stream.
+  int form = s.fused_form;
+  if (form == 0) form = (ctx->stream == ctx->side_stream && ctx->side_stream) ? 2 : 1;
+  if (const char* e = getenv("HB_ARN_ROWS")) form = atoi(e) != 0 ? 2 : 1;
+  if (publish) form = 2;                               // only the warp-per-row form publishes ready words
+  const bool by_rows = form == 2 && cols <= 32 * ARW_VEC * 8;
+  const int per = (int)(rows / s.world);
+  s.ready_rows = 0;
+  p.ready_rows = 0;
   if (by_rows) {
-    const int per = (int)(rows / s.world);
     int grid = (per + AR_THREADS / 32 - 1) / (AR_THREADS / 32);
     int cap = ctx->sm_count < AR_MAX_CTAS ? ctx->sm_count : AR_MAX_CTAS;
+    if (s.fused_ctas >= 1 && s.fused_ctas < cap) cap = s.fused_ctas;
     if (const char* e = getenv("HB_ARN_CTAS")) {      // every rank must use the same value
       const int v = atoi(e);
       if (v >= 1 && v < cap) cap = v;
@@ -854,6 +921,20 @@ extern "C" hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const 
     if (grid > cap) grid = cap;
     p.stagger = algo == HB_AR_NVLS ? 1 : 0;
     if (const char* e = getenv("HB_ARN_STAGGER")) p.stagger = atoi(e) != 0;
+    if (publish) {
+      // rows per ready word: at most 256 (a matmul row tile), a multiple of the eight rows a CTA
+      // handles per round, dividing every rank's share
+      int rb = per >= 256 ? 256 : per;
+      while (rb > 8 && per % rb) rb >>= 1;
+      const int rounds = (per + grid * (AR_THREADS / 32) - 1) / (grid * (AR_THREADS / 32));
+      if (rb % (AR_THREADS / 32) == 0 && per % rb == 0 && rows / rb <= AR_MAX_READY && rounds <= ARW_ROUNDS) {
+        p.ready_rows = rb;
+        s.ready_rows = rb;
+        s.ready_epoch = p.ar.epoch;
+        s.ready_out = out;
+        s.ready_total_rows = rows;
+      }
+    }
     if (algo == HB_AR_NVLS) hb_allreduce_norm_rows_kernel<true, 1><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
     else if (s.world == 2) hb_allreduce_norm_rows_kernel<false, 2><<<grid, AR_THREADS, 0, ctx->stream>>>(p);
     else if (s.world <= 4) hb_allreduce_norm_rows_kernel<false, 4><<<grid, AR_THREADS, 0, ctx->stream>>>(p);

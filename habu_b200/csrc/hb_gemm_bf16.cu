@@ -39,7 +39,42 @@ struct GemmParams {
   int epilogue;
   int a_mn, b_mn;           // operand is MN-major
   int32_t* status;
+  // A's rows arrive while the kernel runs (the gathered output of a fused collective): the
+  // producer waits for the "rows ready" word of a row block before its first load from it.
+  const uint32_t* ready;    // null: A is complete at launch
+  uint32_t ready_epoch;     // a word is set when (int32)(word - ready_epoch) >= 0
+  uint32_t ready_spin;      // polls before the wait gives up
+  int ready_rows;           // rows per word
+  int perm_world, perm_rank;  // > 1: M-tiles are visited owner by owner in turn, this rank's rows first
 };
+
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Waits until rows [m0, m0 + nrows) of A have been published.  `seen` caches the last block
+// found ready (tiles of one M-tile follow each other).  The rows were written by other GPUs
+// (or through the switch) with generic stores; the loads that follow go through the async
+// proxy, hence the proxy fence after the acquire.
+__device__ __forceinline__ bool wait_rows_ready(const GemmParams& p, int m0, int nrows, int& seen, volatile int* abort_flag) {
+  const int last_row = min(m0 + nrows, p.M) - 1;
+  if (last_row < m0) return true;
+  const int b0 = m0 / p.ready_rows, b1 = last_row / p.ready_rows;
+  bool polled = false;
+  for (int b = b0; b <= b1; ++b) {
+    if (b == seen) continue;
+    uint32_t it = 0;
+    while (static_cast<int32_t>(ld_acquire_sys_u32(p.ready + b) - p.ready_epoch) < 0) {
+      if (++it > p.ready_spin || ((it & 255u) == 0 && *abort_flag)) { *abort_flag = 1; return false; }
+      __nanosleep(100);
+    }
+    seen = b;
+    polled = true;
+  }
+  if (polled) asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
+}
 
 // A ring stage holds KPS consecutive 64-wide k-blocks of both operands (KPS = 2: a 128-wide
 // K step per barrier round trip, half as many producer/consumer hand-offs).
@@ -71,6 +106,12 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& 
   const int in_group = tile - group * per_group;
   tm = first_m + in_group % rows;
   tn = in_group / rows;
+  if (p.perm_world > 1) {
+    // visiting index -> M-tile: owners in turn (this rank first), block by block within an owner
+    const int per_owner = p.tiles_m / p.perm_world;
+    const int owner = (tm % p.perm_world + p.perm_rank) % p.perm_world;
+    tm = owner * per_owner + tm / p.perm_world;
+  }
 }
 
 __device__ __forceinline__ float gelu_erf(float x) {
@@ -203,10 +244,15 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int seen = -1;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, p, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        if (p.ready && !wait_rows_ready(p, m0, BM, seen, abort_flag)) {
+          if (p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 4; }
+          break;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(bar_empty + s * 8, phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_arrive_expect_tx(bar_full + s * 8, L::A_BYTES + L::B_BYTES);
@@ -406,11 +452,16 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int seen = -1;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
         tile_coords(tile, p, tm, tn);
         const int m0 = tm * 256 + static_cast<int>(cta_rank) * 128;
         const int n0 = tn * BN2 + static_cast<int>(cta_rank) * (BN2 / 2);
+        if (p.ready && !wait_rows_ready(p, m0, 128, seen, abort_flag)) {
+          if (p.status) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 14; }
+          break;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(bar_empty + s * 8, phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t full_leader = mapa(bar_full + s * 8, 0);
@@ -522,14 +573,16 @@ struct GemmVariant {
   int stages;       // ring depth
   int kps;          // 64-wide k-blocks per ring stage (tile K = 64 * kps)
 };
-// Every kernel instantiation in the library; the ring depths are the ones that fit 227 KB of
-// shared memory (bytes per stage = kps * 128 * (128 + bn) for one CTA, kps * 128 * (128 + bn / 2)
-// per CTA of a pair).
+// Every kernel instantiation in the library (bytes per stage = kps * 128 * (128 + bn) for one
+// CTA, kps * 128 * (128 + bn / 2) per CTA of a pair).  No ring exceeds 192 KB: a seven-stage
+// 256 x 256 pair ring (224 KB) measured within 0.5 % of the six-stage one, and it leaves no
+// shared memory for a collective kernel's CTA on the same SM, which is what the overlapped
+// schedules of the tensor-parallel block rely on.
 constexpr GemmVariant kVariants[] = {
     {1, 256, 4, 1}, {1, 256, 3, 1}, {1, 256, 2, 2},
     {1, 128, 6, 1}, {1, 128, 4, 1}, {1, 128, 3, 2},
     {1, 64, 8, 1},  {1, 64, 5, 1},  {1, 64, 4, 2},
-    {2, 256, 6, 1}, {2, 256, 7, 1}, {2, 256, 5, 1}, {2, 256, 3, 2},
+    {2, 256, 6, 1}, {2, 256, 5, 1}, {2, 256, 4, 1}, {2, 256, 3, 2},
     {2, 128, 8, 1}, {2, 128, 6, 1}, {2, 128, 4, 2},
 };
 constexpr int kRasters[] = {8, 16, 4, 2};        // M-tiles per sweep over N
@@ -652,12 +705,19 @@ hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id)
   p.epilogue = a.epilogue;
   p.a_mn = a.a_mn_major; p.b_mn = a.b_mn_major;
   p.status = ctx->d_status;
+  p.ready = a.ready; p.ready_epoch = a.ready_epoch; p.ready_spin = a.ready_spin; p.ready_rows = a.ready_rows;
+  p.perm_world = 0; p.perm_rank = 0;
+  if (a.ready && a.perm_world > 1) {
+    const int tile_rows = cfg.cluster == 2 ? 256 : BM;
+    const int64_t tiles_m = (a.M + tile_rows - 1) / tile_rows;
+    if (a.M % tile_rows == 0 && tiles_m % a.perm_world == 0) { p.perm_world = a.perm_world; p.perm_rank = a.perm_rank; }
+  }
 #define HB_CASE1(BN, ST, KP) if (cfg.cluster == 1 && cfg.bn == BN && cfg.stages == ST && cfg.kps == KP) return launch_cfg<BN, ST, KP>(ctx, tmA, tmB, p)
 #define HB_CASE2(BN, ST, KP) if (cfg.cluster == 2 && cfg.bn == BN && cfg.stages == ST && cfg.kps == KP) return launch_pair<BN, ST, KP>(ctx, tmA, tmB, p)
   HB_CASE1(256, 4, 1); HB_CASE1(256, 3, 1); HB_CASE1(256, 2, 2);
   HB_CASE1(128, 6, 1); HB_CASE1(128, 4, 1); HB_CASE1(128, 3, 2);
   HB_CASE1(64, 8, 1);  HB_CASE1(64, 5, 1);  HB_CASE1(64, 4, 2);
-  HB_CASE2(256, 6, 1); HB_CASE2(256, 7, 1); HB_CASE2(256, 5, 1); HB_CASE2(256, 3, 2);
+  HB_CASE2(256, 6, 1); HB_CASE2(256, 5, 1); HB_CASE2(256, 4, 1); HB_CASE2(256, 3, 2);
   HB_CASE2(128, 8, 1); HB_CASE2(128, 6, 1); HB_CASE2(128, 4, 2);
 #undef HB_CASE1
 #undef HB_CASE2

@@ -384,9 +384,17 @@ extern "C" hb_status hb_graph_plan(hb_graph* g, size_t* arena_bytes, size_t* sym
         for (int j = i - 1; j >= 0; --j) {
           if ((g->nodes[j].stream != 0) == (g->nodes[i].stream != 0)) continue;
           bool conflict = false;
-          for (const Range& a : foot[i])
-            for (const Range& b : foot[j])
+          // a gathered matmul is ordered behind the collective that writes its A by the "rows
+          // ready" words, not by an event: that one pair of ranges is no conflict
+          const bool by_words = g->nodes[i].kind == HB_NODE_MATMUL && g->nodes[i].iparam[2] != 0 &&
+                                g->nodes[j].kind == HB_NODE_AR_NORM;
+          for (size_t ai = 0; ai < foot[i].size(); ++ai)
+            for (size_t bi = 0; bi < foot[j].size(); ++bi) {
+              const Range& a = foot[i][ai];
+              const Range& b = foot[j][bi];
+              if (by_words && ai == 0 && bi + 1 == foot[j].size()) continue;
               if ((a.write || b.write) && a.lo < b.hi && b.lo < a.hi) conflict = true;
+            }
           if (conflict) { g->wait_for[i] = j; g->needs_event[j] = 1; break; }   // the latest one covers earlier ones
         }
       }
@@ -424,7 +432,7 @@ static hb_status run_node(hb_graph* g, int i) {
           o.residual = T(n.in[2]).ptr;
           o.residual_ld = T(n.in[2]).stride[0];
         }
-        st = hb_matmul(ctx, &a, &b, &c, &o);
+        st = n.iparam[2] ? hb_matmul_gathered(ctx, &a, &b, &c, &o) : hb_matmul(ctx, &a, &b, &c, &o);
         break;
       }
       case HB_NODE_ATTENTION: {

@@ -45,7 +45,16 @@ struct hb_p2p_state {
   bool external = false;              // buffer and mappings are owned by the caller
   uint32_t epoch = 0;
   uint32_t spin_limit = 1u << 24;     // polls per cross-GPU flag wait before HB_ERR_TIMEOUT
+  // "rows ready" words of the last hb_all_reduce_norm (see hb_matmul_gathered): rows per word
+  // (0: none), the epoch they carry, the gathered tensor they describe and its row count
+  int fused_form = 0, fused_ctas = 0; // hb_comm_configure: kernel form of the fused collective, CTA cap of the warp-per-row form
+  int ready_rows = 0;
+  uint32_t ready_epoch = 0;
+  const void* ready_out = nullptr;
+  int64_t ready_total_rows = 0;
 };
+// Byte offset of the ready words inside the flag block that follows the payload.
+size_t hb_p2p_ready_offset();
 
 struct hb_ctx {
   int device = 0;
@@ -116,6 +125,10 @@ struct hb_gemm_args {
   int epilogue;
   const void* residual;
   int64_t ldr;
+  // rows of A published block by block while the kernel runs (see hb_matmul_gathered)
+  const uint32_t* ready;
+  uint32_t ready_epoch, ready_spin;
+  int ready_rows, perm_world, perm_rank;
 };
 hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id);
 hb_status hb_launch_gemm_f32(hb_ctx* ctx, const hb_gemm_args& a);

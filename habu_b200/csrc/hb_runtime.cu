@@ -322,6 +322,36 @@ extern "C" hb_status hb_matmul(hb_ctx* ctx, const hb_tensor* A, const hb_tensor*
   return hb_launch_gemm_bf16(ctx, g, cfg);
 }
 
+// Matmul whose A is the gathered output of the hb_all_reduce_norm call enqueued just before it
+// (on any stream of this context).  The collective publishes one "rows ready" word per block of
+// rows as the rows land; this kernel's loader waits for the word of a block before its first
+// load from it and visits the row blocks owner by owner, this rank's own rows first, so the
+// product of the rows that have arrived runs while the rest are still crossing NVLink.  It may
+// therefore be enqueued on a stream that does NOT wait for the collective.
+extern "C" hb_status hb_matmul_gathered(hb_ctx* ctx, const hb_tensor* A, const hb_tensor* B, hb_tensor* C,
+                                        const hb_matmul_opts* opts) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (ctx->world <= 1 || ctx->p2p.world <= 1) return hb_matmul(ctx, A, B, C, opts);
+  hb_gemm_args g;
+  hb_status st = decode_matmul(ctx, A, B, C, opts, &g);
+  if (st != HB_OK) return st;
+  const hb_p2p_state& s = ctx->p2p;
+  if (A->dtype != HB_BF16 || g.a_mn_major || (g.lda & 7) || (g.ldb & 7) || hb_gemm_skinny_applicable(g))
+    return hb_fail(ctx, HB_ERR_UNSUPPORTED, "matmul_gathered: needs a row-major bf16 A with more than 64 rows");
+  if (s.ready_rows <= 0 || s.ready_out != A->ptr || s.ready_total_rows != g.M)
+    return hb_fail(ctx, HB_ERR_INVALID,
+                   "matmul_gathered: A is not the output of the hb_all_reduce_norm enqueued before this call "
+                   "(or that call published no ready words)");
+  g.ready = reinterpret_cast<const uint32_t*>(static_cast<const char*>(s.local) + s.bytes + hb_p2p_ready_offset());
+  g.ready_epoch = s.ready_epoch;
+  g.ready_spin = s.spin_limit;
+  g.ready_rows = s.ready_rows;
+  g.perm_world = s.world;
+  g.perm_rank = s.rank;
+  const int cfg = (opts && opts->config_id >= 0) ? opts->config_id : hb_gemm_pick_config(ctx, g);
+  return hb_launch_gemm_bf16(ctx, g, cfg);
+}
+
 hb_status hb_host_pipe(hb_ctx* ctx, int n, cudaEvent_t** events) {
   HB_CUDA(ctx, cudaSetDevice(ctx->device));
   if (!ctx->h2d_stream) HB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));

@@ -62,8 +62,10 @@ class Graph:
         self.ctx._check(_lib.hb_graph_add(self._h, C.byref(n)))
         return out
 
-    def matmul(self, a, b, out, epilogue=_capi.HB_EPI_NONE, residual=None, config_id=-1):
-        return self._add(NODE_MATMUL, [a, b, residual], out, [epilogue, config_id])
+    def matmul(self, a, b, out, epilogue=_capi.HB_EPI_NONE, residual=None, config_id=-1, gathered=False):
+        """gathered=True: `a` is the output of the all_reduce_norm node added just before; the
+        product waits for its rows block by block instead of for the end of the collective."""
+        return self._add(NODE_MATMUL, [a, b, residual], out, [epilogue, config_id, int(gathered)])
 
     def attention(self, q, k, v, out, causal=True, scale=None, lse=None):
         if scale is None:
@@ -76,11 +78,12 @@ class Graph:
         return self._add(NODE_ALL_REDUCE, [], x, [algo], stream=stream)
 
     def all_reduce_norm(self, partial, gain, residual_in, residual_out, out, eps=1e-5, gather_only=False,
-                        algo=_capi.HB_AR_AUTO, stream=0):
+                        algo=_capi.HB_AR_AUTO, stream=0, ready_words=False):
         """Fused reduce-scatter + residual add + RMSNorm + all-gather (gather_only: publish the
-        updated residual rows instead of their norm).  stream=1: on the side stream."""
-        return self._add(NODE_AR_NORM, [partial, gain, residual_in, residual_out], out, [int(gather_only), algo], [eps],
-                         stream=stream)
+        updated residual rows instead of their norm).  stream=1: on the side stream.
+        ready_words: publish a word per block of gathered rows for a ``matmul(..., gathered=True)``."""
+        return self._add(NODE_AR_NORM, [partial, gain, residual_in, residual_out], out,
+                         [int(gather_only) | (2 if ready_words else 0), algo], [eps], stream=stream)
 
     def rmsnorm(self, x, gain, out, residual=None, eps=1e-5):
         return self._add(NODE_RMSNORM, [x, gain, residual], out, [], [eps])

@@ -331,6 +331,11 @@ class Context:
         arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in peer_ptrs])
         self._check(_lib.hb_p2p_attach_external(self._h, world, rank, arr, C.c_void_p(multicast_ptr or 0), nbytes))
 
+    def comm_configure(self, fused_form: int = 0, fused_ctas: int = 0):
+        """Kernel form of the fused collective: 0 automatic, 1 CTA per row, 2 warp per row on at
+        most `fused_ctas` CTAs (the form that runs beside a GEMM)."""
+        self._check(_lib.hb_comm_configure(self._h, fused_form, fused_ctas))
+
     def comm_set_wait_limit(self, polls: int):
         """Polls per cross-GPU flag wait before a collective kernel reports HB_ERR_TIMEOUT."""
         self._check(_lib.hb_comm_set_wait_limit(self._h, polls))

@@ -94,12 +94,19 @@ class DecoderGraph:
     """
 
     def __init__(self, ctx, cfg: DecoderConfig, world: int, rank: int, layers: List[Dict[str, np.ndarray]],
-                 algo: int = _capi.HB_AR_AUTO, chunks: int = 1, fused: bool = False):
+                 algo: int = _capi.HB_AR_AUTO, chunks: int = 1, fused: bool = False, gathered: bool = False,
+                 fused_form: int = 0, fused_ctas: int = 0, share=None):
+        """`fused_form` / `fused_ctas`: kernel form of the fused collective for this graph's runs
+        (``Context.comm_configure``).  `share`: another DecoderGraph of the same rank whose uploaded
+        weights and input buffer this one reuses (schedule variants of one model)."""
         from .graph import Graph
         check_shardable(cfg, world)
         self._out_id = None
+        self.fused_form, self.fused_ctas, self._share = fused_form, fused_ctas, share
+        self.schedule = {"chunks": chunks, "fused": bool(fused and world > 1), "gathered": bool(gathered and world > 1),
+                         "fused_form": fused_form, "fused_ctas": fused_ctas}
         if fused and world > 1:
-            self._build_fused(ctx, cfg, world, rank, layers, algo, chunks)
+            self._build_fused(ctx, cfg, world, rank, layers, algo, chunks, gathered)
             return
         if cfg.batch % chunks:
             raise ValueError(f"batch {cfg.batch} does not split into {chunks} chunks")
@@ -111,7 +118,7 @@ class DecoderGraph:
         Tc = Bc * cfg.seq                   # tokens per chunk
         side = 1 if (chunks > 1 and world > 1) else 0
         g = self.graph = Graph(ctx)
-        self.x0 = ctx.empty((T, d))
+        self.x0 = share.x0 if share is not None else ctx.empty((T, d))
         self._out = ctx.empty((T, d))
         x0, out = g.input(self.x0), g.input(self._out)
         rows = lambda t, c: g.view(t, c * Tc * d, (Tc, d), (d, 1))       # chunk c of a [T, d] tensor
@@ -119,7 +126,7 @@ class DecoderGraph:
         x = None                                  # residual stream [T, d], planner-owned after layer 0
         pending = [None] * chunks                 # per chunk: sublayer output not yet added into the stream
         for li, lw in enumerate(layers):
-            dev = {k: ctx.upload(v) for k, v in lw.items()}
+            dev = share.weights[li] if share is not None else {k: ctx.upload(v) for k, v in lw.items()}
             self.weights.append(dev)
             w = {k: g.input(v if k in ("g1", "g2") else v.T) for k, v in dev.items()}
             first = x is None
@@ -163,7 +170,7 @@ class DecoderGraph:
             g.add(rows(x, c), pending[c], rows(out, c))
         self.symmetric_needed = None
 
-    def _build_fused(self, ctx, cfg, world, rank, layers, algo, chunks=1):
+    def _build_fused(self, ctx, cfg, world, rank, layers, algo, chunks=1, gathered=False):
         """Sequence-parallel form: each allreduce + residual add + RMSNorm becomes one fused
         node (reduce-scatter, add and norm on this rank's rows, all-gather of the normalised
         rows); the residual stream is sharded by rows and gathered once at the end.
@@ -174,8 +181,15 @@ class DecoderGraph:
         executor's side stream and crosses NVLink while the tensor cores work on block c+1
         (and, later, on the consumer of block c).  A rank owns rows/world rows of EVERY block,
         so the sharding of the residual stream is the same in all collectives.  The values do
-        not depend on ``chunks``: every output row is computed by the same arithmetic."""
+        not depend on ``chunks``: every output row is computed by the same arithmetic.
+
+        With ``gathered`` (one row block only) the fused collectives go to the side stream and
+        the column-parallel product that consumes their gathered rows is not ordered behind them
+        by an event: it waits block by block for the "rows ready" words the collective publishes
+        and starts with this rank's own rows, so the all-gather runs under the product."""
         from .graph import Graph
+        if gathered and chunks != 1:
+            raise ValueError("gathered products take the whole gathered tensor: chunks must be 1")
         if cfg.tokens % (world * chunks):
             raise ValueError("tokens must split evenly over the ranks and row blocks")
         self.ctx, self.cfg, self.world, self.rank, self.chunks = ctx, cfg, world, rank, chunks
@@ -183,11 +197,12 @@ class DecoderGraph:
         ql, kl, fl = cfg.n_q_heads // world, cfg.n_kv_heads // world, cfg.ffn_hidden // world
         W = (ql + 2 * kl) * hd
         Tc = T // chunks
-        side = 1 if chunks > 1 else 0
+        side = 1 if (chunks > 1 or gathered) else 0
         g = self.graph = Graph(ctx)
-        self.x0 = ctx.empty((T, d))
+        share = self._share
+        self.x0 = share.x0 if share is not None else ctx.empty((T, d))
         x0 = g.input(self.x0)
-        self.weights = [{k: ctx.upload(v) for k, v in lw.items()} for lw in layers]
+        self.weights = share.weights if share is not None else [{k: ctx.upload(v) for k, v in lw.items()} for lw in layers]
         ws = [{k: g.input(v if k in ("g1", "g2") else v.T) for k, v in dev.items()} for dev in self.weights]
         rows = lambda t, c, n: g.view(t, c * Tc * n, (Tc, n), (n, 1)) if chunks > 1 else t   # row block c of a [T, n] tensor
         x = g.temp((T, d))                          # residual stream: only this rank's rows of each block are live
@@ -200,7 +215,7 @@ class DecoderGraph:
         for li, w in enumerate(ws):
             qkv = g.temp((T, W))
             for c in range(chunks):                 # block c starts as soon as its gathered rows have landed
-                g.matmul(rows(h, c, d), w["wqkv"], rows(qkv, c, W))
+                g.matmul(rows(h, c, d), w["wqkv"], rows(qkv, c, W), gathered=gathered and li > 0)
             g.rope(g.view(qkv, 0, (T, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
             g.rope(g.view(qkv, ql * hd, (T, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
             v4 = lambda off, H: g.view(qkv, off, (cfg.batch, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
@@ -211,14 +226,15 @@ class DecoderGraph:
             for c in range(chunks):
                 g.matmul(rows(attn, c, ql * hd), w["wo"], rows(ao, c, d))
                 g.all_reduce_norm(rows(ao, c, d), w["g2"], rows(xin, c, d), rows(x, c, d), rows(h2, c, d), eps=cfg.eps,
-                                  algo=algo, stream=side)
+                                  algo=algo, stream=side, ready_words=gathered)
             act = g.temp((T, fl))
             last = li + 1 == len(ws)
             for c in range(chunks):
-                g.matmul(rows(h2, c, d), w["wgu"], rows(act, c, fl), epilogue=_capi.HB_EPI_SWIGLU)
+                g.matmul(rows(h2, c, d), w["wgu"], rows(act, c, fl), epilogue=_capi.HB_EPI_SWIGLU, gathered=gathered)
                 g.matmul(rows(act, c, fl), w["wd"], rows(fo, c, d))
                 g.all_reduce_norm(rows(fo, c, d), None if last else ws[li + 1]["g1"], rows(x, c, d), rows(x, c, d),
-                                  rows(nxt, c, d), eps=cfg.eps, gather_only=last, algo=algo, stream=side)
+                                  rows(nxt, c, d), eps=cfg.eps, gather_only=last, algo=algo, stream=side,
+                                  ready_words=gathered and not last)
             if last:
                 self._out_id = nxt
             else:
@@ -238,7 +254,36 @@ class DecoderGraph:
         return arena, sym
 
     def run(self):
+        if self.world > 1:
+            self.ctx.comm_configure(self.fused_form, self.fused_ctas)
         self.graph.run()
+
+
+# Schedules of the tensor-parallel block worth timing on a given box: how the fused collectives
+# overlap the products around them.  Which one wins depends on the rank count (at 2 GPUs the
+# collectives are a quarter of the step, at 8 more than half) and on the NVLink fabric.
+#   - one row block, collectives on the main stream (nothing overlaps; fastest collective kernel);
+#   - two row blocks: the collective of block c on the side stream under the products of block c+1
+#     (warp-per-row form, few CTAs, beside the GEMM on the same SMs);
+#   - one row block, gathered products: the column-parallel product after each collective waits
+#     for its rows block by block and runs under the all-gather.
+def candidate_schedules(world: int):
+    if world <= 1:
+        return [dict(chunks=1, fused=False)]
+    return [dict(chunks=1, fused=True, fused_form=1),
+            dict(chunks=2, fused=True, fused_form=2, fused_ctas=64),
+            dict(chunks=2, fused=True, fused_form=2, fused_ctas=128),
+            dict(chunks=2, fused=True, fused_form=1),
+            dict(chunks=1, fused=True, gathered=True, fused_form=2, fused_ctas=128),
+            dict(chunks=1, fused=True, gathered=True, fused_form=2, fused_ctas=64)]
+
+
+def pick_schedule(graphs, measure):
+    """Times every candidate graph with `measure(run) -> ms` (the caller's device timer; with
+    several ranks it must return the same number on all of them, e.g. the maximum) and returns
+    (index of the fastest, all timings)."""
+    times = [float(measure(g.run)) for g in graphs]
+    return int(np.argmin(times)), times
 
 
 def decode_layer(full: Dict[str, np.ndarray], cfg: DecoderConfig) -> Dict[str, np.ndarray]:

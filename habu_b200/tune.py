@@ -15,11 +15,11 @@ import sys
 CACHE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tune_cache.txt")
 
 # (M, N, K, layout, epilogue): bench GEMMs, the decoder's projections at TP 1/2/4/8 (also per
-# micro-batch of 2048 tokens) and the MLP's forward / dW / dX products.
+# row block of 4096 and 2048 tokens) and the MLP's forward / dW / dX products.
 def default_shapes():
     shapes = [(1024, 1024, 1024, 0, 0), (4096, 4096, 4096, 0, 0), (8192, 8192, 8192, 0, 0)]
     for tp in (1, 2, 4, 8):
-        for T in (8192, 2048):
+        for T in (8192, 4096, 2048):
             shapes += [(T, 6144 // tp, 4096, 0, 0), (T, 4096, 4096 // tp, 0, 0),
                        (T, 2 * 14336 // tp, 4096, 0, 2), (T, 4096, 14336 // tp, 0, 0)]
     shapes += [(4096, 8192, 8192, 0, 0), (8192, 8192, 4096, 3, 0), (4096, 8192, 8192, 2, 0)]

@@ -95,6 +95,14 @@ typedef struct hb_matmul_opts {
 } hb_matmul_opts;
 hb_status hb_matmul(hb_ctx* ctx, const hb_tensor* A, const hb_tensor* B, hb_tensor* C,
                     const hb_matmul_opts* opts);
+/* Same node for an A that is the gathered output of the hb_all_reduce_norm call enqueued just
+ * before it: the loader waits block by block for the rows to land ("rows ready" words the
+ * collective publishes) and visits this rank's own rows first, so the call may be enqueued on
+ * a stream that does not wait for the collective and the product overlaps the all-gather.
+ * Needs row-major bf16 A with more than 64 rows; with one rank it is hb_matmul.  No
+ * reference counterpart. */
+hb_status hb_matmul_gathered(hb_ctx* ctx, const hb_tensor* A, const hb_tensor* B, hb_tensor* C,
+                             const hb_matmul_opts* opts);
 /* Same node with HOST buffers: uploads A and B, runs, downloads C, synchronises.
  * A is [M,K] row-major, B is column-major (K contiguous per column), C row-major. */
 hb_status hb_matmul_host(hb_ctx* ctx, const void* A_host, const void* B_host, void* C_host,
@@ -232,6 +240,13 @@ hb_status hb_all_reduce(hb_ctx* ctx, void* data, int64_t count, int32_t dtype, i
  * No reference counterpart (the reference reports failures as `Result` values,
  * `src/lib/error.ml:18-26`, and never waits on a device). */
 hb_status hb_comm_set_wait_limit(hb_ctx* ctx, uint32_t polls);
+/* Kernel form of hb_all_reduce_norm.  fused_form 1: one CTA per row, the faster form when the
+ * collective has the GPU to itself; 2: one warp per row on at most `fused_ctas` CTAs (0 = one
+ * per SM), small enough to run beside a GEMM on the same SMs, the form for collectives that
+ * overlap compute; 0 (default): form 1 on the context's own stream, form 2 on its side stream.
+ * The results are the same bits in every form.  Every rank must make the same choice.
+ * No reference counterpart. */
+hb_status hb_comm_configure(hb_ctx* ctx, int32_t fused_form, int32_t fused_ctas);
 /* Overlap: hb_all_reduce_async enqueues the same allreduce on the context's high-priority
  * side stream, ordered after everything already queued on the main stream, and returns;
  * hb_side_join makes the main stream wait for the side stream.  Kernels queued between the
@@ -244,7 +259,9 @@ hb_status hb_side_join(hb_ctx* ctx);
  * (HB_AR_NVLS), bf16.  `partial` and `out` are [rows, cols] inside the symmetric buffer;
  * `residual_in` / `residual_out` are local [rows, cols] of which only this rank's rows are
  * read / written: residual_out = bf16(residual_in + bf16(sum of partials)).
- * mode 0: out = rmsnorm(residual_out) * gain; mode 1: out = residual_out (final gather). */
+ * mode 0: out = rmsnorm(residual_out) * gain; mode 1: out = residual_out (final gather).
+ * Adding 2 to `mode` makes the call publish one "rows ready" word per block of gathered rows
+ * as the rows land, which is what hb_matmul_gathered waits for (warp-per-row form only). */
 hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const void* gain,
                              const void* residual_in, void* residual_out, void* out,
                              int64_t rows, int64_t cols, float eps, int32_t mode, int32_t algo);
@@ -258,7 +275,8 @@ hb_status hb_all_reduce_norm(hb_ctx* ctx, const void* partial, const void* gain,
  * variant-tagged definitions dispatched in order (`lift_defs_exn`, tree.ml:786-811). */
 typedef struct hb_graph hb_graph;
 enum {
-  HB_NODE_MATMUL = 0,      /* in: A, B, [residual]      iparam: epilogue, config_id          */
+  HB_NODE_MATMUL = 0,      /* in: A, B, [residual]      iparam: epilogue, config_id, gathered (1: A is the
+                              output of the preceding all_reduce_norm node; hb_matmul_gathered)   */
   HB_NODE_ATTENTION = 1,   /* in: Q, K, V, [lse]        iparam: causal        fparam: scale   */
   HB_NODE_ALL_REDUCE = 2,  /* in place on `out`         iparam: algorithm                     */
   HB_NODE_RMSNORM = 3,     /* in: x, gain, [residual]                         fparam: eps     */

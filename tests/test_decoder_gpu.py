@@ -92,10 +92,11 @@ def _tp_rank(rank, world, nvls):
     outs, graphs = {}, {}
     if nvls:
         cases = [("nvls", hb.HB_AR_NVLS, 1), ("nvls-fused", hb.HB_AR_NVLS, 1), ("nvls-fused-pipelined", hb.HB_AR_NVLS, 2),
-                 ("p2p-fused", hb.HB_AR_P2P, 1)]
+                 ("nvls-fused-gathered", hb.HB_AR_NVLS, 1), ("p2p-fused", hb.HB_AR_P2P, 1)]
     else:
         cases = [("nccl", hb.HB_AR_NCCL, 1), ("p2p", hb.HB_AR_AUTO, 1), ("p2p-overlap", hb.HB_AR_AUTO, 2),
-                 ("p2p-fused", hb.HB_AR_AUTO, 1), ("p2p-fused-pipelined", hb.HB_AR_AUTO, 2)]
+                 ("p2p-fused", hb.HB_AR_AUTO, 1), ("p2p-fused-pipelined", hb.HB_AR_AUTO, 2),
+                 ("p2p-fused-gathered", hb.HB_AR_AUTO, 1)]
     have = True
     with guard:
         ctx = hb.Context(rank)
@@ -110,7 +111,7 @@ def _tp_rank(rank, world, nvls):
         need = 0
         for name, algo, chunks in cases:
             dg = DecoderGraph(ctx, CFG, world, rank, [_bits(shard_layer(l, CFG, world, rank)) for l in layers], algo, chunks,
-                              fused="fused" in name)
+                              fused="fused" in name, gathered="gathered" in name)
             _, sym = dg.plan()
             need = max(need, sym)
             graphs[name] = dg
@@ -162,12 +163,16 @@ def _tp_rank(rank, world, nvls):
         if not guard.agree():
             break
     with guard:
+        if ok and nvls and len(outs) == len(cases):
+            assert np.array_equal(outs["nvls-fused"], outs["nvls-fused-gathered"]), "the gathered products changed the result"
         if ok and not nvls and len(outs) == len(cases):
             assert np.array_equal(outs["p2p"], outs["p2p-overlap"]), "chunked overlap changed the result"
             # the fused reduce-scatter / norm / all-gather nodes round at the same points
             assert np.array_equal(outs["p2p"], outs["p2p-fused"]), "fused collective changed the result"
             # row blocks pipelined over two streams: same arithmetic per row, same bits
             assert np.array_equal(outs["p2p"], outs["p2p-fused-pipelined"]), "pipelined row blocks changed the result"
+            # products that wait for their gathered rows word by word: same arithmetic again
+            assert np.array_equal(outs["p2p"], outs["p2p-fused-gathered"]), "the gathered products changed the result"
     # same tear-down on every rank: drain, close, and only then let the mappings go
     if ctx is not None:
         for dg in graphs.values():
