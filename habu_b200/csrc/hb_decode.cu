@@ -62,6 +62,8 @@ __global__ void __launch_bounds__(DEC_THREADS)
 hb_attention_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint8_t dec_smem_raw[];
   DecSmem& sm = *reinterpret_cast<DecSmem*>(dec_smem_raw);
+  // the attention-out product behind this kernel may start streaming its weights in
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const int G = p.G;
@@ -294,10 +296,22 @@ extern "C" hb_status hb_attention_decode(hb_ctx* ctx, const void* qkv, int64_t r
   if (batch * n_kv_heads > HB_MAX_SPLITK_TILES || batch > 65535 || n_kv_heads > 65535)
     return hb_fail(ctx, HB_ERR_UNSUPPORTED, "attention_decode: batch * kv_heads exceeds %d", HB_MAX_SPLITK_TILES);
   if (len_hint <= 0 || len_hint > s_max) len_hint = s_max;
-  // enough splits for about three CTAs per SM, each at least one tile long
+  static int resident_per_sm[64] = {};
+  if (!resident_per_sm[ctx->device & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(hb_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(attention_decode)");
+    int n = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, hb_attention_decode_kernel, DEC_THREADS, sizeof(DecSmem));
+    if (e != cudaSuccess || n < 1) { cudaGetLastError(); n = 1; }
+    resident_per_sm[ctx->device & 63] = n;
+  }
+  // As many splits as fill the GPU ONCE: every CTA streams an equal share of the cache, so a
+  // grid that is a little larger than what is resident at one time (512 CTAs on 444 slots)
+  // runs a nearly empty second wave and takes twice as long.  Each split is at least one tile.
   const int64_t groups = batch * n_kv_heads;
   const int64_t tiles = (len_hint + DEC_TILE - 1) / DEC_TILE;
-  int64_t splits = (3 * (int64_t)ctx->sm_count + groups - 1) / groups;
+  const int64_t slots = (int64_t)ctx->sm_count * resident_per_sm[ctx->device & 63];
+  int64_t splits = slots / groups;
   if (splits > tiles) splits = tiles;
   if (splits < 1) splits = 1;
   if (splits > 256) splits = 256;
@@ -326,12 +340,6 @@ extern "C" hb_status hb_attention_decode(hb_ctx* ctx, const void* qkv, int64_t r
   p.chunk = (int)chunk_tiles * DEC_TILE;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = ctx->d_status;
-  static bool attr_set[64] = {};
-  if (!attr_set[ctx->device & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(hb_attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecSmem));
-    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(attention_decode)");
-    attr_set[ctx->device & 63] = true;
-  }
   hb_attention_decode_kernel<<<dim3((unsigned)splits, (unsigned)n_kv_heads, (unsigned)batch), DEC_THREADS, sizeof(DecSmem),
                                ctx->stream>>>(p);
   ctx->launches++;

@@ -10,7 +10,14 @@
 //     so every SM streams the same number of bytes and pays one prologue;
 //   * a range that covers only part of a tile writes its fp32 partial to scratch; the last
 //     range to finish a tile (atomic ticket) adds the partials in k order -- a fixed order,
-//     so the result is bit-identical run to run -- rounds to bf16 once and writes C.
+//     so the result is bit-identical run to run -- rounds to bf16 once and writes C;
+//   * programmatic dependent launch: B holds weights, which no kernel of a step writes, so the
+//     loader fills the whole ring with B before it waits for the kernel in front of it on the
+//     stream (whose output is A, a few KB); in a generation step the weights of the next
+//     product stream in while the small kernels between the products (norm, RoPE, attention
+//     over the cache, SwiGLU) are still running.  Everything that depends on that kernel -- the
+//     A loads, the partials, tickets and C -- comes after the wait.  B must not be written by
+//     the kernel directly in front of this one on the stream.
 // Scratch: tiles * max_segments * 128 * Mpad floats of partials plus one ticket per tile
 // (tickets are left at zero by the CTA that consumes them).
 // Algorithmic traffic per launch: (N*K + M*K + M*N) * 2 bytes.
@@ -105,6 +112,7 @@ hb_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  grid_launch_dependents();     // the next kernel on the stream may begin its own prologue
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -112,7 +120,27 @@ hb_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_cons
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t u = u_begin; u < u_end; ++u) {
+      // Ring fill: B (weights) of the first `stages` units before the dependency wait, their A
+      // after it.  The slots are empty at start, so no wait on `empty` is needed here.
+      const int64_t n_units = u_end - u_begin;
+      const int fill = static_cast<int>(n_units < p.stages ? n_units : p.stages);
+      for (int i = 0; i < fill; ++i) {
+        const int64_t u = u_begin + i;
+        const int tile = static_cast<int>(u / p.num_kb);
+        const int kb = static_cast<int>(u % p.num_kb);
+        mbar_arrive_expect_tx(bar_full + i * 8, (B_BYTES + p.a_bytes) * p.kps);
+        for (int x = 0; x < p.kps; ++x)
+          tma_load_2d(sB + i * b_stride + x * B_BYTES, &tmB, bar_full + i * 8, (kb * p.kps + x) * BK, tile * BN_ROWS);
+      }
+      grid_dependency_wait();
+      for (int i = 0; i < fill; ++i) {
+        const int kb = static_cast<int>((u_begin + i) % p.num_kb);
+        for (int x = 0; x < p.kps; ++x)
+          tma_load_2d(sA + i * a_stride + x * a_box, &tmA, bar_full + i * 8, (kb * p.kps + x) * BK, 0);
+      }
+      s = fill == p.stages ? 0 : fill;
+      phase = fill == p.stages ? 1 : 0;
+      for (int64_t u = u_begin + fill; u < u_end; ++u) {
         const int tile = static_cast<int>(u / p.num_kb);
         const int kb = static_cast<int>(u % p.num_kb);
         if (!mbar_wait(bar_empty + s * 8, phase ^ 1, abort_flag)) { ok = false; break; }
@@ -164,6 +192,7 @@ hb_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmB, const __grid_cons
     const int etid = (warp - 2) * 32 + lane;     // 0..127
     bool ok = true;
     int seg = 0;
+    grid_dependency_wait();                      // partials, tickets and C may still be in use by the kernel in front
     for (int64_t u = u_begin; u < u_end; ++seg) {
       const int tile = static_cast<int>(u / p.num_kb);
       const int kb0 = static_cast<int>(u % p.num_kb);
@@ -348,7 +377,23 @@ hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_g
     if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(skinny gemm)");
     attr_set = true;
   }
-  hb_gemm_skinny_kernel<<<grid, SK_THREADS, skinny_smem_bytes(mpad, p.kps), stream>>>(tmB, tmA, p);
+  // With a context the launch may overlap the tail of the kernel in front of it on the stream
+  // (programmatic dependent launch: see the header of this file); the context-free static entry
+  // point keeps plain stream order.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(SK_THREADS);
+  cfg.dynamicSmemBytes = skinny_smem_bytes(mpad, p.kps);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  bool pdl = ctx != nullptr;
+  if (const char* e = getenv("HB_SKINNY_PDL")) pdl = pdl && atoi(e) != 0;
+  cfg.attrs = &attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t le = cudaLaunchKernelEx(&cfg, hb_gemm_skinny_kernel, tmB, tmA, p);
+  if (le != cudaSuccess) return hb_check_cuda(ctx, le, "skinny gemm launch");
   return hb_check_cuda(ctx, cudaGetLastError(), "skinny gemm launch");
 }
 

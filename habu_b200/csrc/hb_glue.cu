@@ -27,10 +27,15 @@ __device__ __forceinline__ float warp_sum(float v) {
 constexpr int RMS_THREADS = 256;
 constexpr int RMS_MAX_VEC = 8;   // cols <= 256 * 8 * 8 = 16384
 
+// Lets a kernel launched behind this one with the programmatic-stream-serialization attribute
+// (the stream-K matmul: it streams its weights in before it waits for this kernel) start early.
+#define HB_LAUNCH_DEPENDENTS() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain, uint4* __restrict__ y,
                uint4* residual, int cols8, float inv_cols, float eps) {
   __shared__ float red[RMS_THREADS / 32];
+  HB_LAUNCH_DEPENDENTS();
   const int64_t row = blockIdx.x;
   const uint4* xr = x + row * cols8;
   uint4* rr = residual ? residual + row * cols8 : nullptr;
@@ -156,6 +161,7 @@ __device__ __forceinline__ float gelu_f(float v) { return 0.5f * v * (1.0f + erf
 
 // out[r, j] = silu(x[r, j]) * x[r, half + j]; half8 = half / 8
 __global__ void swiglu_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, int64_t rows, int half8) {
+  HB_LAUNCH_DEPENDENTS();
   const int64_t total = rows * half8;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
@@ -177,6 +183,7 @@ template <int OP>  // 0 gelu(x), 1 a + b, 2 gelu'(a) * b
 __global__ void ew_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out,
                           int64_t n8, const __nv_bfloat16* at, const __nv_bfloat16* bt, __nv_bfloat16* ot,
                           int tail) {
+  HB_LAUNCH_DEPENDENTS();
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < n8;
        idx += (int64_t)gridDim.x * blockDim.x) {
     const uint4 av = a[idx];

@@ -112,6 +112,14 @@ __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity,
   return false;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it on the stream is still running; grid_dependency_wait() returns once that
+// kernel has completed and its writes are visible (at once when there is no such dependency).
+// grid_launch_dependents() lets the next such kernel start its own prologue early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- cluster helpers
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
