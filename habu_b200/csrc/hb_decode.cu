@@ -23,17 +23,20 @@
 namespace {
 
 constexpr int DD = 128;            // head_dim
-constexpr int DEC_TILE = 64;       // cached positions per shared-memory tile
+constexpr int DEC_TILE = 64;       // cached positions per shared-memory tile (16 per warp)
+constexpr int DEC_STAGES = 3;      // tiles in flight per CTA
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_MAX_G = 8;       // query heads per KV head
-constexpr int K_ROW = DD + 8;      // bf16 per K row in shared memory (272 B: conflict-free 16-byte reads down a column)
+constexpr int KV_ROW = DD + 8;     // bf16 per K / V row in shared memory: 272 B, so that the eight
+                                   // 16-byte rows of an ldmatrix fall into eight different bank groups
+constexpr float DEC_RESCALE = 8.0f;   // the running reference moves only when the maximum grew by 2^8
 
 struct DecodeParams {
   const __nv_bfloat16* qkv;        // [batch, row_stride]: q heads, then k heads, then v heads of the new token
   const __nv_bfloat16* kv;         // cache
   __nv_bfloat16* out;              // [batch, hq * 128]
   float* part_o;                   // [batch * hkv * splits * G][128]
-  float* part_ml;                  // [batch * hkv * splits * G][2]  (running max in log2 units, sum)
+  float* part_ml;                  // [batch * hkv * splits * G][2]  (reference max in log2 units, sum)
   int* tickets;                    // [batch * hkv], zero between launches
   const int32_t* pos;              // current position: the cache holds pos + 1 tokens
   int64_t row_stride;
@@ -48,16 +51,45 @@ __device__ __forceinline__ void cp_async16(uint32_t smem, const void* g) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D(16x8, fp32) += A(16x16, bf16, row) . B(16x8, bf16, col).  Rows 8..15 of A are padding here
+// (a1 = a3 = 0): the query heads of one KV head, at most eight, are the rows 0..7.
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 
 struct DecSmem {
-  __nv_bfloat16 k[2][DEC_TILE][K_ROW];
-  __nv_bfloat16 v[2][DEC_TILE][DD];
-  float q[DEC_MAX_G][DD];          // queries, pre-multiplied by scale * log2(e)
-  float p[DEC_TILE][DEC_MAX_G];    // scores, then probabilities, of the current tile
-  float alpha[DEC_MAX_G], m[DEC_MAX_G], l[DEC_MAX_G];
+  __nv_bfloat16 k[DEC_STAGES][DEC_TILE][KV_ROW];
+  __nv_bfloat16 v[DEC_STAGES][DEC_TILE][KV_ROW];
+  float wml[DEC_THREADS / 32][DEC_MAX_G][2];      // per-warp (reference max, sum)
   int last;
 };
+// The per-warp partial outputs, merged at the end, reuse the K tiles' memory (the loop is over).
+typedef float DecWarpOut[DEC_MAX_G][DD];
+static_assert(sizeof(DecWarpOut) * (DEC_THREADS / 32) <= sizeof(__nv_bfloat16) * DEC_STAGES * DEC_TILE * KV_ROW, "merge buffer");
 
+// The cache is read once from HBM; the arithmetic (two small products per cached position) would
+// keep the CUDA cores busy three times as long as the read takes, so it runs on the tensor
+// cores: per warp and 16 cached positions S[q, pos] = Q K^T and O[q, :] += P V as m16n8k16 tiles
+// whose 16 rows hold the (at most eight) query heads that share the KV head -- one pass over K
+// and V serves the whole group.  Fragments come from shared memory with ldmatrix (transposed
+// for V); P goes from the S accumulators straight into the A operand of the second product.
+// The four warps of a CTA take a quarter of every 64-position tile each and keep their own
+// running maximum, sum and output, merged at the end in warp order; the CTAs that share a
+// (sequence, KV head) are merged in split order by the last one to finish.
 __global__ void __launch_bounds__(DEC_THREADS)
 hb_attention_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint8_t dec_smem_raw[];
@@ -66,6 +98,7 @@ hb_attention_decode_kernel(const DecodeParams p) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int g = lane >> 2, tq = lane & 3;        // fragment row (query head) and column pair
   const int G = p.G;
   int len = *p.pos + 1;
   if (len > p.s_max) len = p.s_max;        // the append kernel has already reported the overflow
@@ -73,121 +106,136 @@ hb_attention_decode_kernel(const DecodeParams p) {
   const int end = min(begin + p.chunk, len);
   const int64_t slot = (static_cast<int64_t>(b) * p.hkv + hk) * p.splits + split;
 
-  float o[DEC_MAX_G];
+  float o[DD / 8][4];
 #pragma unroll
-  for (int q = 0; q < DEC_MAX_G; ++q) o[q] = 0.f;
-  if (t < DEC_MAX_G) { sm.m[t] = -INFINITY; sm.l[t] = 0.f; sm.alpha[t] = 1.f; }
+  for (int n = 0; n < DD / 8; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  float m_ref = -INFINITY, l = 0.f;
 
   if (begin < end) {
-    // queries of this KV head's group -> shared memory, scaled
-    for (int i = t; i < G * DD; i += DEC_THREADS) {
-      const int q = i / DD, d = i - q * DD;
-      sm.q[q][d] = __bfloat162float(p.qkv[b * p.row_stride + static_cast<int64_t>(hk * G + q) * DD + d]) * p.scale_log2;
+    // A fragments of Q for the eight 16-wide chunks of the head dimension: row g = query head g
+    uint32_t qa[DD / 16][2];
+    {
+      const __nv_bfloat16* qrow = p.qkv + b * p.row_stride + static_cast<int64_t>(hk * G + g) * DD;
+#pragma unroll
+      for (int c = 0; c < DD / 16; ++c) {
+        qa[c][0] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + 16 * c + 2 * tq) : 0u;
+        qa[c][1] = g < G ? *reinterpret_cast<const uint32_t*>(qrow + 16 * c + 8 + 2 * tq) : 0u;
+      }
     }
     const __nv_bfloat16* kbase = p.kv + (static_cast<int64_t>(b) * p.s_max * p.hkv + hk) * DD;
     const __nv_bfloat16* vbase = p.kv + (static_cast<int64_t>(p.batch + b) * p.s_max * p.hkv + hk) * DD;
     const int64_t pos_stride = static_cast<int64_t>(p.hkv) * DD;
     const int n_tiles = (end - begin + DEC_TILE - 1) / DEC_TILE;
-    auto load_tile = [&](int tile, int buf) {
-      const int p0 = begin + tile * DEC_TILE;
-      // 64 rows x 16 chunks of 16 B for K and for V; rows past the end repeat the last valid row
-      // (they are masked below; the cache beyond `len` may hold anything, NaN patterns included)
+    auto load_tile = [&](int tile) {
+      if (tile < n_tiles) {
+        const int buf = tile % DEC_STAGES;
+        const int p0 = begin + tile * DEC_TILE;
+        // 64 rows x 16 chunks of 16 B for K and for V; rows past the end repeat the last valid row
+        // (they are masked below; the cache beyond `len` may hold anything, NaN patterns included)
 #pragma unroll
-      for (int i = 0; i < (DEC_TILE * 16) / DEC_THREADS; ++i) {
-        const int idx = t + i * DEC_THREADS;
-        const int r = idx >> 4, c = idx & 15;
-        const int pos = min(p0 + r, end - 1);
-        cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(&sm.k[buf][r][c * 8])), kbase + pos * pos_stride + c * 8);
-        cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(&sm.v[buf][r][c * 8])), vbase + pos * pos_stride + c * 8);
+        for (int i = 0; i < (DEC_TILE * 16) / DEC_THREADS; ++i) {
+          const int idx = t + i * DEC_THREADS;
+          const int r = idx >> 4, c = idx & 15;
+          const int pos = min(p0 + r, end - 1);
+          cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(&sm.k[buf][r][c * 8])), kbase + pos * pos_stride + c * 8);
+          cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(&sm.v[buf][r][c * 8])), vbase + pos * pos_stride + c * 8);
+        }
       }
-      cp_async_commit();
+      cp_async_commit();                                 // an empty group keeps the count uniform
     };
-    load_tile(0, 0);
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) load_tile(s);
     for (int tile = 0; tile < n_tiles; ++tile) {
-      const int buf = tile & 1;
-      if (tile + 1 < n_tiles) { load_tile(tile + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-      __syncthreads();                                   // tile `buf` (and, first time, q) visible to all
-      // ---- scores: thread = (position r, query parity)
-      {
-        const int r = t & (DEC_TILE - 1), par = t >> 6;
-        float acc[DEC_MAX_G / 2];
+      cp_async_wait<DEC_STAGES - 2>();
+      __syncthreads();                                   // tile landed; everyone is done with the buffer refilled next
+      load_tile(tile + DEC_STAGES - 1);
+      const int buf = tile % DEC_STAGES;
+      const int r0 = warp * 16;                          // this warp's 16 positions of the tile
+      // ---- S = Q K^T: two 8-position column blocks
+      float sacc[2][4];
 #pragma unroll
-        for (int j = 0; j < DEC_MAX_G / 2; ++j) acc[j] = 0.f;
-#pragma unroll 4
-        for (int c = 0; c < DD / 8; ++c) {
-          const uint4 k8 = *reinterpret_cast<const uint4*>(&sm.k[buf][r][c * 8]);
-          const uint32_t kw[4] = {k8.x, k8.y, k8.z, k8.w};
-          float kf[8];
+      for (int nb = 0; nb < 2; ++nb) {
+        sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kw[j]));
-            kf[2 * j] = f.x; kf[2 * j + 1] = f.y;
-          }
-#pragma unroll
-          for (int j = 0; j < DEC_MAX_G / 2; ++j) {
-            const int q = par + 2 * j;
-            if (q < G) {
-              const float4 q0 = *reinterpret_cast<const float4*>(&sm.q[q][c * 8]);
-              const float4 q1 = *reinterpret_cast<const float4*>(&sm.q[q][c * 8 + 4]);
-              acc[j] += kf[0] * q0.x + kf[1] * q0.y + kf[2] * q0.z + kf[3] * q0.w + kf[4] * q1.x + kf[5] * q1.y +
-                        kf[6] * q1.z + kf[7] * q1.w;
-            }
-          }
-        }
-        const bool valid = begin + tile * DEC_TILE + r < end;
-#pragma unroll
-        for (int j = 0; j < DEC_MAX_G / 2; ++j) {
-          const int q = par + 2 * j;
-          if (q < G) sm.p[r][q] = valid ? acc[j] : -INFINITY;
+        for (int i = 0; i < DD / 32; ++i) {
+          uint32_t kf[4];
+          ldsm_x4(static_cast<uint32_t>(__cvta_generic_to_shared(&sm.k[buf][r0 + 8 * nb + (lane & 7)][32 * i + 8 * (lane >> 3)])), kf);
+          mma_16816(sacc[nb], qa[2 * i][0], qa[2 * i][1], kf[0], kf[1]);
+          mma_16816(sacc[nb], qa[2 * i + 1][0], qa[2 * i + 1][1], kf[2], kf[3]);
         }
       }
-      __syncthreads();
-      // ---- online softmax: warp w owns queries w and w + 4
-      for (int q = warp; q < G; q += DEC_THREADS / 32) {
-        const float s0 = sm.p[lane][q], s1 = sm.p[lane + 32][q];
-        float mx = fmaxf(s0, s1);
+      // ---- online softmax for query head g (lanes with g < G): positions r0 + 8 nb + 2 tq, + 1
+      const int pg = begin + tile * DEC_TILE + r0 + 2 * tq;
+      float sv[4];
 #pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o2));
-        const float m_old = sm.m[q];
-        const float m_new = fmaxf(m_old, mx);            // finite: every tile holds a valid position
-        const float p0 = exp2f(s0 - m_new), p1 = exp2f(s1 - m_new);
-        float sum = p0 + p1;
+      for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o2);
-        sm.p[lane][q] = p0;
-        sm.p[lane + 32][q] = p1;
-        if (lane == 0) {
-          const float a = exp2f(m_old - m_new);          // 0 on the first tile (m_old = -inf)
-          sm.alpha[q] = a;
-          sm.l[q] = sm.l[q] * a + sum;
-          sm.m[q] = m_new;
+        for (int e = 0; e < 2; ++e)
+          sv[2 * nb + e] = (pg + 8 * nb + e < end) ? sacc[nb][e] * p.scale_log2 : -INFINITY;
+      float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const bool need = mx > m_ref + DEC_RESCALE || (m_ref == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, need)) {
+        if (need) {
+          const float f = m_ref == -INFINITY ? 0.f : exp2f(m_ref - mx);
+          l *= f;
+#pragma unroll
+          for (int n = 0; n < DD / 8; ++n) { o[n][0] *= f; o[n][1] *= f; }
+          m_ref = mx;
         }
       }
-      __syncthreads();
-      // ---- O += P V: thread = output dimension d
-      {
+      float pv[4];
 #pragma unroll
-        for (int q = 0; q < DEC_MAX_G; ++q)
-          if (q < G) o[q] *= sm.alpha[q];
-#pragma unroll 8
-        for (int r = 0; r < DEC_TILE; ++r) {
-          const float v = __bfloat162float(sm.v[buf][r][t]);
-          const float4 pa = *reinterpret_cast<const float4*>(&sm.p[r][0]);
-          const float4 pb = *reinterpret_cast<const float4*>(&sm.p[r][4]);
-          const float pr[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
-#pragma unroll
-          for (int q = 0; q < DEC_MAX_G; ++q)
-            if (q < G) o[q] += pr[q] * v;
-        }
+      for (int e = 0; e < 4; ++e) {
+        pv[e] = m_ref == -INFINITY ? 0.f : exp2f(sv[e] - m_ref);     // masked positions: exp2(-inf) = 0
+        l += pv[e];
       }
-      __syncthreads();                                   // tile `buf` and p[] are free again
+      const uint32_t pa0 = g < G ? pack2_bf16(pv[0], pv[1]) : 0u;     // positions 2 tq, 2 tq + 1
+      const uint32_t pa2 = g < G ? pack2_bf16(pv[2], pv[3]) : 0u;     // positions 8 + 2 tq, + 1
+      // ---- O += P V: sixteen 8-wide column blocks of the head dimension
+#pragma unroll
+      for (int n = 0; n < DD / 16; ++n) {
+        uint32_t vf[4];
+        ldsm_x4_trans(static_cast<uint32_t>(__cvta_generic_to_shared(
+                          &sm.v[buf][r0 + 8 * ((lane >> 3) & 1) + (lane & 7)][16 * n + 8 * (lane >> 4)])), vf);
+        mma_16816(o[2 * n], pa0, pa2, vf[0], vf[1]);
+        mma_16816(o[2 * n + 1], pa0, pa2, vf[2], vf[3]);
+      }
     }
+    cp_async_wait<0>();
   }
-  // ---- this split's partial result
-  for (int q = 0; q < G; ++q) p.part_o[(slot * G + q) * DD + t] = o[q];
-  if (t < G) {
-    p.part_ml[(slot * G + t) * 2] = sm.m[t];
-    p.part_ml[(slot * G + t) * 2 + 1] = sm.l[t];
+  // ---- merge the four warps (warp order), then publish this split's partial result
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  __syncthreads();                                       // every warp has read its last tile
+  DecWarpOut* wo = reinterpret_cast<DecWarpOut*>(&sm.k[0][0][0]);
+  if (g < G) {
+#pragma unroll
+    for (int n = 0; n < DD / 8; ++n) {
+      wo[warp][g][8 * n + 2 * tq] = o[n][0];
+      wo[warp][g][8 * n + 2 * tq + 1] = o[n][1];
+    }
+    if (tq == 0) { sm.wml[warp][g][0] = m_ref; sm.wml[warp][g][1] = l; }
+  }
+  __syncthreads();
+  for (int q = 0; q < G; ++q) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) M = fmaxf(M, sm.wml[w][q][0]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) {
+      const float lw = sm.wml[w][q][1];
+      const float wgt = lw > 0.f ? exp2f(sm.wml[w][q][0] - M) : 0.f;
+      L += lw * wgt;
+      acc += wo[w][q][t] * wgt;
+    }
+    p.part_o[(slot * G + q) * DD + t] = acc;
+    if (t == 0) {
+      p.part_ml[(slot * G + q) * 2] = M;
+      p.part_ml[(slot * G + q) * 2 + 1] = L;
+    }
   }
   __threadfence();
   __syncthreads();
