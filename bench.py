@@ -41,8 +41,8 @@ NVSMI_Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
 # (profiles/), scaled to the full launch; None where not captured.
-NCU_TRAFFIC_BYTES = {"gemm": 1.128998e9 + 127.475712e6, "skinny": 134.593280e6 + 4.446208e6,
-                     "attention": 805.502464e6 + 257.930496e6}
+NCU_TRAFFIC_BYTES = {"gemm": 1.059352e9 + 127.465216e6, "skinny": 134.590976e6 + 4.355840e6,
+                     "attention": 806.299392e6 + 255.520768e6}
 
 
 def peaks():
@@ -763,6 +763,13 @@ def main():
     import habu_b200 as hb
 
     torch.cuda.set_device(local_rank)
+    # The launcher pins OMP_NUM_THREADS=1 for its workers.  The CPU side of a run (seeded inputs
+    # and weights on every rank, the parity checks on rank 0, all outside the timed regions) would
+    # then take minutes on one thread: rank 0 uses every core, the others share them.
+    import oracle
+    cores = oracle.use_all_cores()
+    if rank != 0:
+        oracle.set_num_threads(max(1, cores // world))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     stream = torch.cuda.Stream()

@@ -85,6 +85,12 @@ def use_all_cores() -> int:
     return num_threads()
 
 
+def set_num_threads(n: int) -> int:
+    """Use `n` threads (at least one); returns the thread count now in use."""
+    _lib.orc_set_num_threads(C.c_int(max(1, int(n))))
+    return num_threads()
+
+
 def round_bf16(x: np.ndarray) -> np.ndarray:
     """Round fp32 values to bf16 (nearest-even) in place; returns x."""
     _lib.orc_round_bf16(_f(x), _i64(x.size))
