@@ -392,7 +392,8 @@ class DecoderWorkload:
             kinds[k][0] += 1
             kinds[k][1] += float(t)
         return {"per_kind_us": {k: {"nodes": n, "us": round(t, 1)} for k, (n, t) in kinds.items()},
-                "serial_sum_us": round(float(acc.sum()), 1), "nodes": len(lines)}
+                "serial_sum_us": round(float(acc.sum()), 1), "nodes": len(lines),
+                "per_node_us": [[l.split()[1], round(float(t), 1)] for l, t in zip(lines, acc)]}
 
     def cpu_sample(self):
         """Bounded CPU sample: the same block at batch 1 x seq 256 on the oracle (fp32)."""

@@ -98,6 +98,7 @@ def load() -> C.CDLL:
         "hb_argmax": [vp, vp, vp, i64, i64],
         "hb_mse": [vp, vp, vp, vp, vp, i64],
         "hb_adam_step": [vp, vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, i64, f32],
+        "hb_adam_step_async": [vp, vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, i64, f32],
         "hb_comm_unique_id": [vp],
         "hb_comm_init_rank": [vp, i32, i32, vp],
         "hb_comm_destroy": [vp],

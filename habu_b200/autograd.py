@@ -13,6 +13,7 @@ strided views: ``dX = dY @ W`` reads W as an N-contiguous B operand and
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
 
 import numpy as np
@@ -44,10 +45,12 @@ class Tape:
         return loss
 
     # -- backward -------------------------------------------------------------------
-    def backward(self, scratch: List[Tensor], on_grad=None):
+    def backward(self, scratch: List[Tensor], on_grad=None, on_layer_done=None):
         """Launches the gradient kernels.  `scratch` holds two [B, width] bf16 buffers used
         alternately for activation gradients.  `on_grad(grad_w)` is called right after each
-        weight gradient is enqueued (the data-parallel trainer sums it there)."""
+        weight gradient is enqueued (the data-parallel trainer sums it there);
+        `on_layer_done(grad_w)` once both products of a linear layer are enqueued, i.e. when
+        nothing queued later reads that layer's weights (the trainer updates them there)."""
         ctx = self.ctx
         grads = {}                      # id(tensor) -> gradient tensor
         k = 0
@@ -75,6 +78,8 @@ class Tape:
                     # dX[B, in] = dY[B, out] @ W[out, in]
                     ctx.matmul(dout, w, out=ctx.wrap(dx.ptr, x.shape))
                     grads[id(x)] = ctx.wrap(dx.ptr, x.shape)
+                if on_layer_done:
+                    on_layer_done(grad_w)
         self.ops.clear()
 
 
@@ -87,6 +92,7 @@ class MlpTrainer:
         self.ctx, self.width, self.batch, self.n, self.world = ctx, width, batch, n_layers, world
         self.lr, self.b1, self.b2, self.eps, self.algo = lr, beta1, beta2, eps, algo
         self.step_no = 0
+        self.overlap_update = os.environ.get("HB_MLP_OVERLAP_UPDATE", "1") != "0"   # Adam under the backward products
         from .model_ir import f32_to_bf16_bits as to_bf16_bits
         self.w32 = [ctx.upload(np.ascontiguousarray(w, np.float32)) for w in weights_f32]
         self.wb = [ctx.upload(to_bf16_bits(w)) for w in weights_f32]
@@ -121,13 +127,20 @@ class MlpTrainer:
         # each weight gradient is summed across ranks on the side stream while the main stream
         # goes on with the remaining backward products
         on_grad = (lambda g: ctx.all_reduce_async(g, self.algo)) if self.world > 1 else None
-        tape.backward(self.scratch, on_grad)
-        if self.world > 1:
-            ctx.side_join()
         self.step_no += 1
-        for i in range(self.n):
+        layer_of = {id(g): i for i, g in enumerate(self.grads)}
+
+        # The optimizer step of a layer is bound by HBM, the backward products by the tensor cores:
+        # as soon as both products of a layer are enqueued (nothing later reads its weights), its
+        # update goes to the side stream -- behind that layer's gradient sum, which is on the same
+        # stream -- and runs under the products of the layers still to come.
+        def update(grad_w):
+            i = layer_of[id(grad_w)]
             ctx.adam_step(self.w32[i], self.m[i], self.v[i], self.grads[i], self.wb[i], self.step_no, self.lr, self.b1,
-                          self.b2, self.eps, 1.0 / self.world)
+                          self.b2, self.eps, 1.0 / self.world, on_side_stream=self.overlap_update)
+        tape.backward(self.scratch, on_grad, update)
+        if self.world > 1 or self.overlap_update:
+            ctx.side_join()
         return self.loss
 
     # -- checkpoint / resume ----------------------------------------------------------

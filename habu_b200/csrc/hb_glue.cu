@@ -457,9 +457,47 @@ extern "C" hb_status hb_adam_step(hb_ctx* ctx, float* w, float* m, float* v, con
     return hb_fail(ctx, HB_ERR_INVALID, "adam: misaligned pointer");
   const float c1 = (float)(1.0 - pow((double)beta1, (double)step));
   const float c2 = (float)(1.0 - pow((double)beta2, (double)step));
+  // The update may run on the side stream beside the backward products (hb_adam_step_async): it
+  // then shares SMs with GEMM CTAs, which only works under the GEMM's L1 / shared-memory split.
+  static bool carve_set[64] = {};
+  if (!carve_set[ctx->device & 63]) {
+    cudaFuncSetAttribute(adam_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaGetLastError();
+    carve_set[ctx->device & 63] = true;
+  }
   adam_kernel<<<grid_for(ctx, n / 4, 256), 256, 0, ctx->stream>>>(
       reinterpret_cast<float4*>(w), reinterpret_cast<float4*>(m), reinterpret_cast<float4*>(v),
       static_cast<const uint2*>(grad_bf16), static_cast<uint2*>(w_bf16), n / 4, lr, beta1, beta2, eps, c1, c2, grad_scale);
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "adam launch");
+}
+
+// The same update on the context's high-priority side stream, ordered after everything queued on
+// the main stream so far (like hb_all_reduce_async; hb_side_join makes the main stream wait).
+// The optimizer step is bound by HBM (30 bytes per weight) and the backward products by the
+// tensor cores, so the update of a layer whose gradient is complete runs under the products of
+// the layers still to come.  Kernels queued on the main stream between this call and
+// hb_side_join must not touch the layer's weights, moments or gradient.
+extern "C" hb_status hb_adam_step_async(hb_ctx* ctx, float* w, float* m, float* v, const void* grad_bf16, void* w_bf16,
+                                        int64_t n, float lr, float beta1, float beta2, float eps, int64_t step,
+                                        float grad_scale) {
+  if (!ctx) return HB_ERR_INVALID;
+  if (!ctx->side_stream) {
+    int lo = 0, hi = 0;
+    cudaDeviceGetStreamPriorityRange(&lo, &hi);
+    cudaError_t e = cudaStreamCreateWithPriority(&ctx->side_stream, cudaStreamNonBlocking, hi);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaStreamCreate(side)");
+  }
+  if (!ctx->side_event) {
+    cudaError_t e = cudaEventCreateWithFlags(&ctx->side_event, cudaEventDisableTiming);
+    if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaEventCreate(side)");
+  }
+  cudaStream_t main_stream = ctx->stream;
+  cudaError_t e = cudaEventRecord(ctx->side_event, main_stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->side_stream, ctx->side_event, 0);
+  if (e != cudaSuccess) return hb_check_cuda(ctx, e, "adam_step_async: fork");
+  ctx->stream = ctx->side_stream;
+  const hb_status st = hb_adam_step(ctx, w, m, v, grad_bf16, w_bf16, n, lr, beta1, beta2, eps, step, grad_scale);
+  ctx->stream = main_stream;
+  return st;
 }

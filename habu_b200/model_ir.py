@@ -290,9 +290,12 @@ class Context:
         return loss, dy
 
     def adam_step(self, w: Tensor, m: Tensor, v: Tensor, grad: Tensor, w_bf16: Tensor, step: int, lr=1e-3, beta1=0.9,
-                  beta2=0.999, eps=1e-8, grad_scale=1.0):
-        self._check(_lib.hb_adam_step(self._h, w.ptr, m.ptr, v.ptr, grad.ptr, w_bf16.ptr, w.nbytes // 4, lr, beta1,
-                                      beta2, eps, step, grad_scale))
+                  beta2=0.999, eps=1e-8, grad_scale=1.0, on_side_stream: bool = False):
+        """on_side_stream: enqueue the update on the side stream behind everything queued so far
+        (pair with side_join()), so that it runs under the products that follow."""
+        fn = _lib.hb_adam_step_async if on_side_stream else _lib.hb_adam_step
+        self._check(fn(self._h, w.ptr, m.ptr, v.ptr, grad.ptr, w_bf16.ptr, w.nbytes // 4, lr, beta1, beta2, eps, step,
+                       grad_scale))
 
     def argmax(self, x: Tensor) -> Tensor:
         rows, cols = x.shape

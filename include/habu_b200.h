@@ -206,6 +206,12 @@ hb_status hb_mse(hb_ctx* ctx, const void* y, const void* target, void* dy, float
 hb_status hb_adam_step(hb_ctx* ctx, float* w, float* m, float* v, const void* grad_bf16,
                        void* w_bf16, int64_t n, float lr, float beta1, float beta2, float eps,
                        int64_t step, float grad_scale);
+/* The same update enqueued on the context's side stream behind everything queued so far
+ * (hb_side_join makes the main stream wait for it): the HBM-bound optimizer step of a layer
+ * runs under the tensor-bound backward products of the layers still to come. */
+hb_status hb_adam_step_async(hb_ctx* ctx, float* w, float* m, float* v, const void* grad_bf16,
+                       void* w_bf16, int64_t n, float lr, float beta1, float beta2, float eps,
+                       int64_t step, float grad_scale);
 /* argmax over the last dimension, first index wins ties (bit-exact). */
 hb_status hb_argmax(hb_ctx* ctx, const void* x, int32_t* out, int64_t rows, int64_t cols);
 

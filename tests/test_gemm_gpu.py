@@ -156,3 +156,32 @@ def test_invalid_arguments_are_reported_not_launched(ctx):
     with pytest.raises(hb.HabuError):
         ctx.matmul(a, a.T, config_id=999)
     ctx.sync()
+
+
+def test_gathered_entry_point_is_the_plain_matmul_on_one_rank(ctx):
+    """hb_matmul_gathered waits for rows that a fused collective on other ranks publishes; with a
+    single rank there is nothing to wait for and it must be the plain matmul, bit for bit."""
+    import ctypes as C
+    from habu_b200 import _capi, model_ir
+    M, N, K = 512, 384, 256
+    A, Ab = bf16_normal((M, K), SEED + 900, K ** -0.5)
+    B, Bb = bf16_normal((N, K), SEED + 901)
+    dA, dB = ctx.upload(Ab), ctx.upload(Bb)
+    want = ctx.download(ctx.matmul(dA, dB.T))
+    out = ctx.empty((M, N))
+    ta, tb, tc = dA.c(), dB.T.c(), out.c()
+    opts = _capi.hb_matmul_opts(hb.HB_EPI_NONE, -1, None, 0)
+    ctx._check(model_ir._lib.hb_matmul_gathered(ctx._h, C.byref(ta), C.byref(tb), C.byref(tc), C.byref(opts)))
+    ctx.sync()
+    assert np.array_equal(ctx.download(out), want)
+    assert max_abs(oracle.from_bf16_bits(want), oracle.gemm(A, B.T)) < TOL_BF16
+
+
+def test_comm_configure_validates_its_arguments(ctx):
+    ctx.comm_configure(1, 0)
+    ctx.comm_configure(2, 64)
+    ctx.comm_configure(0, 0)
+    for bad in ((3, 0), (-1, 0), (1, -5)):
+        with pytest.raises(hb.HabuError) as e:
+            ctx.comm_configure(*bad)
+        assert e.value.status == 1
