@@ -296,14 +296,15 @@ class DecoderWorkload:
         # How the collectives overlap the products around them is a schedule choice that depends on
         # the rank count and the fabric: the candidates (habu_b200.tp.candidate_schedules; all
         # compute the same values) are timed here, outside the timed region, and the fastest one
-        # is what the step runs.  HB_DECODER_SCHEDULE=i pins candidate i; HB_DECODER_FUSED=0 and
-        # HB_DECODER_CHUNKS=n select the unfused allreduce graph as before.
+        # is what the step runs.  HB_DECODER_SCHEDULE=i pins candidate i; HB_DECODER_GATHERED=1 adds
+        # the gathered-product schedules; HB_DECODER_FUSED=0 and HB_DECODER_CHUNKS=n select the
+        # unfused allreduce graph as before.
         from habu_b200.tp import candidate_schedules, pick_schedule
         if os.environ.get("HB_DECODER_FUSED", "1") != "1" or "HB_DECODER_CHUNKS" in os.environ:
             cands = [dict(chunks=int(os.environ.get("HB_DECODER_CHUNKS", "1")),
                           fused=os.environ.get("HB_DECODER_FUSED", "1") == "1")]
         else:
-            cands = candidate_schedules(world)
+            cands = candidate_schedules(world, gathered=os.environ.get("HB_DECODER_GATHERED") == "1")
             if "HB_DECODER_SCHEDULE" in os.environ:
                 cands = [cands[int(os.environ["HB_DECODER_SCHEDULE"])]]
         graphs = []

@@ -267,15 +267,19 @@ class DecoderGraph:
 #     (warp-per-row form, few CTAs, beside the GEMM on the same SMs);
 #   - one row block, gathered products: the column-parallel product after each collective waits
 #     for its rows block by block and runs under the all-gather.
-def candidate_schedules(world: int):
+def candidate_schedules(world: int, gathered: bool = False):
+    """`gathered` adds the gathered-product schedules (measured slower than two row blocks at 2
+    GPUs: 3.73 against 3.29 ms; not measured on more)."""
     if world <= 1:
         return [dict(chunks=1, fused=False)]
-    return [dict(chunks=1, fused=True, fused_form=1),
-            dict(chunks=2, fused=True, fused_form=2, fused_ctas=64),
-            dict(chunks=2, fused=True, fused_form=2, fused_ctas=128),
-            dict(chunks=2, fused=True, fused_form=1),
-            dict(chunks=1, fused=True, gathered=True, fused_form=2, fused_ctas=128),
-            dict(chunks=1, fused=True, gathered=True, fused_form=2, fused_ctas=64)]
+    out = [dict(chunks=1, fused=True, fused_form=1),
+           dict(chunks=2, fused=True, fused_form=2, fused_ctas=64),
+           dict(chunks=2, fused=True, fused_form=2, fused_ctas=128),
+           dict(chunks=2, fused=True, fused_form=1)]
+    if gathered:
+        out += [dict(chunks=1, fused=True, gathered=True, fused_form=2, fused_ctas=128),
+                dict(chunks=1, fused=True, gathered=True, fused_form=2, fused_ctas=64)]
+    return out
 
 
 def pick_schedule(graphs, measure):
