@@ -19,6 +19,7 @@ HB_F32, HB_BF16, HB_I32 = 0, 1, 2
 HB_EPI_NONE, HB_EPI_GELU, HB_EPI_SWIGLU, HB_EPI_RESIDUAL = 0, 1, 2, 3
 HB_AR_AUTO, HB_AR_NCCL, HB_AR_P2P, HB_AR_NVLS = 0, 1, 2, 3
 HB_OP_MATMUL, HB_OP_ATTENTION = 0, 1
+HB_MATMUL_WEIGHTS_B = 0x100
 HB_TUNE_CACHED, HB_TUNE_SEARCH = 0, 1
 HB_UNIQUE_ID_BYTES = 128
 HB_IPC_HANDLE_BYTES = 64

@@ -94,8 +94,9 @@ __global__ void __launch_bounds__(DEC_THREADS)
 hb_attention_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint8_t dec_smem_raw[];
   DecSmem& sm = *reinterpret_cast<DecSmem*>(dec_smem_raw);
-  // the attention-out product behind this kernel may start streaming its weights in
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // programmatic dependent launch: wait for the kernel in front (RoPE + append) before the first
+  // memory access; the attention-out product behind this kernel may start streaming its weights in
+  asm volatile("griddepcontrol.wait;\n\tgriddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const int g = lane >> 2, tq = lane & 3;        // fragment row (query head) and column pair
@@ -267,6 +268,7 @@ hb_attention_decode_kernel(const DecodeParams p) {
 // One thread per rotation pair of a query or key head, plus one per 16-byte chunk of a value head.
 __global__ void hb_rope_append_kernel(__nv_bfloat16* qkv, __nv_bfloat16* kv, const int32_t* pos_ptr, int batch, int hq,
                                       int hkv, int s_max, int64_t row_stride, double log2_base, int32_t* status) {
+  asm volatile("griddepcontrol.wait;\n\tgriddepcontrol.launch_dependents;" ::: "memory");   // see hb_launch_dependent
   const int pos = *pos_ptr;
   if (pos < 0 || pos >= s_max) {                          // cache full: report, write nothing
     if (blockIdx.x == 0 && threadIdx.x == 0 && status) { atomicCAS(status, 0, HB_ERR_INVALID); status[1] = HB_KTAG_DECODE; status[2] = pos; }
@@ -322,7 +324,7 @@ extern "C" hb_status hb_rope_append(hb_ctx* ctx, void* qkv, int64_t row_stride, 
   const int64_t work = batch * (n_q_heads + n_kv_heads) * (DD / 2) + batch * n_kv_heads * (DD / 8);
   if (work > INT32_MAX || 2 * batch * s_max * n_kv_heads * DD > (int64_t(1) << 40))
     return hb_fail(ctx, HB_ERR_UNSUPPORTED, "rope_append: problem too large");
-  hb_rope_append_kernel<<<(unsigned)((work + 255) / 256), 256, 0, ctx->stream>>>(
+  hb_launch_dependent(hb_rope_append_kernel, dim3((unsigned)((work + 255) / 256)), dim3(256), 0, ctx->stream,
       static_cast<__nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(kv_cache), pos_dev, (int)batch, (int)n_q_heads,
       (int)n_kv_heads, (int)s_max, row_stride, log2((double)base), ctx->d_status);
   ctx->launches++;
@@ -388,8 +390,8 @@ extern "C" hb_status hb_attention_decode(hb_ctx* ctx, const void* qkv, int64_t r
   p.chunk = (int)chunk_tiles * DEC_TILE;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = ctx->d_status;
-  hb_attention_decode_kernel<<<dim3((unsigned)splits, (unsigned)n_kv_heads, (unsigned)batch), DEC_THREADS, sizeof(DecSmem),
-                               ctx->stream>>>(p);
+  hb_launch_dependent(hb_attention_decode_kernel, dim3((unsigned)splits, (unsigned)n_kv_heads, (unsigned)batch),
+                      dim3(DEC_THREADS), sizeof(DecSmem), ctx->stream, p);
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "attention_decode launch");
 }

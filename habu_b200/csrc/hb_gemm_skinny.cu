@@ -16,8 +16,9 @@
 //     stream (whose output is A, a few KB); in a generation step the weights of the next
 //     product stream in while the small kernels between the products (norm, RoPE, attention
 //     over the cache, SwiGLU) are still running.  Everything that depends on that kernel -- the
-//     A loads, the partials, tickets and C -- comes after the wait.  B must not be written by
-//     the kernel directly in front of this one on the stream.
+//     A loads, the partials, tickets and C -- comes after the wait.  Only launches whose caller
+//     says that B is a weight matrix (HB_MATMUL_WEIGHTS_B) are made that way; any other keeps
+//     plain stream order (the wait then returns at once).
 // Scratch: tiles * max_segments * 128 * Mpad floats of partials plus one ticket per tile
 // (tickets are left at zero by the CTA that consumes them).
 // Algorithmic traffic per launch: (N*K + M*K + M*N) * 2 bytes.
@@ -377,9 +378,9 @@ hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_g
     if (e != cudaSuccess) return hb_check_cuda(ctx, e, "cudaFuncSetAttribute(skinny gemm)");
     attr_set = true;
   }
-  // With a context the launch may overlap the tail of the kernel in front of it on the stream
-  // (programmatic dependent launch: see the header of this file); the context-free static entry
-  // point keeps plain stream order.
+  // A launch whose B is a weight matrix may overlap the tail of the kernel in front of it on the
+  // stream (programmatic dependent launch: see the header of this file); every other launch, and
+  // the context-free static entry point, keeps plain stream order.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(SK_THREADS);
@@ -388,7 +389,7 @@ hb_status hb_launch_gemm_skinny_raw(hb_ctx* ctx, cudaStream_t stream, const hb_g
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
-  bool pdl = ctx != nullptr;
+  bool pdl = ctx != nullptr && a.b_is_weights;
   if (const char* e = getenv("HB_SKINNY_PDL")) pdl = pdl && atoi(e) != 0;
   cfg.attrs = &attr;
   cfg.numAttrs = pdl ? 1 : 0;

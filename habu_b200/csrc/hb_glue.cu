@@ -27,9 +27,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 constexpr int RMS_THREADS = 256;
 constexpr int RMS_MAX_VEC = 8;   // cols <= 256 * 8 * 8 = 16384
 
-// Lets a kernel launched behind this one with the programmatic-stream-serialization attribute
-// (the stream-K matmul: it streams its weights in before it waits for this kernel) start early.
-#define HB_LAUNCH_DEPENDENTS() asm volatile("griddepcontrol.launch_dependents;" ::: "memory")
+// Programmatic dependent launch (hb_launch_dependent): wait for the kernel in front before the
+// first memory access, and let the kernel behind (e.g. the stream-K matmul, which streams its
+// weights in before its own wait) start early.
+#define HB_LAUNCH_DEPENDENTS() asm volatile("griddepcontrol.wait;\n\tgriddepcontrol.launch_dependents;" ::: "memory")
 
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain, uint4* __restrict__ y,
@@ -264,7 +265,7 @@ extern "C" hb_status hb_rmsnorm(hb_ctx* ctx, const void* x, const void* gain, vo
   if (!HB_ALIGNED16(x) || !HB_ALIGNED16(gain) || !HB_ALIGNED16(y) || !HB_ALIGNED16(residual_inout))
     return hb_fail(ctx, HB_ERR_INVALID, "rmsnorm: pointers must be 16-byte aligned");
   if (rows > INT32_MAX) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "rmsnorm: too many rows");
-  rmsnorm_kernel<<<(unsigned)rows, RMS_THREADS, 0, ctx->stream>>>(
+  hb_launch_dependent(rmsnorm_kernel, dim3((unsigned)rows), dim3(RMS_THREADS), 0, ctx->stream,
       static_cast<const uint4*>(x), static_cast<const uint4*>(gain), static_cast<uint4*>(y),
       static_cast<uint4*>(residual_inout), (int)(cols / 8), 1.0f / (float)cols, eps);
   ctx->launches++;
@@ -326,7 +327,7 @@ extern "C" hb_status hb_swiglu(hb_ctx* ctx, const void* x, void* out, int64_t ro
   if (rows <= 0 || half <= 0) return hb_fail(ctx, HB_ERR_INVALID, "swiglu: empty dimension");
   if (half % 8 || !HB_ALIGNED16(x) || !HB_ALIGNED16(out))
     return hb_fail(ctx, HB_ERR_UNSUPPORTED, "swiglu: half width must be a multiple of 8 and pointers 16-byte aligned");
-  swiglu_kernel<<<grid_for(ctx, rows * (half / 8), 256), 256, 0, ctx->stream>>>(
+  hb_launch_dependent(swiglu_kernel, dim3(grid_for(ctx, rows * (half / 8), 256)), dim3(256), 0, ctx->stream,
       static_cast<const uint4*>(x), static_cast<uint4*>(out), rows, (int)(half / 8));
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "swiglu launch");
@@ -344,7 +345,7 @@ static hb_status launch_ew(hb_ctx* ctx, const char* name, const void* a, const v
   const __nv_bfloat16* at = static_cast<const __nv_bfloat16*>(a) + n8 * 8;
   const __nv_bfloat16* bt = b ? static_cast<const __nv_bfloat16*>(b) + n8 * 8 : nullptr;
   __nv_bfloat16* ot = static_cast<__nv_bfloat16*>(out) + n8 * 8;
-  ew_kernel<OP><<<grid_for(ctx, n8, 256), 256, 0, ctx->stream>>>(
+  hb_launch_dependent(ew_kernel<OP>, dim3(grid_for(ctx, n8, 256)), dim3(256), 0, ctx->stream,
       static_cast<const uint4*>(a), static_cast<const uint4*>(b), static_cast<uint4*>(out), n8, at, bt, ot, tail);
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), name);

@@ -427,7 +427,7 @@ static hb_status run_node(hb_graph* g, int i) {
       case HB_NODE_MATMUL: {
         hb_tensor a = as_tensor(T(n.in[0])), b = as_tensor(T(n.in[1])), c = as_tensor(T(n.out));
         hb_matmul_opts o = {n.iparam[0], n.iparam[1], nullptr, 0};
-        if (n.iparam[0] == HB_EPI_RESIDUAL) {
+        if ((n.iparam[0] & 0xff) == HB_EPI_RESIDUAL) {
           if (n.in[2] < 0) { st = hb_fail(ctx, HB_ERR_INVALID, "graph: residual epilogue without a residual tensor"); break; }
           o.residual = T(n.in[2]).ptr;
           o.residual_ld = T(n.in[2]).stride[0];

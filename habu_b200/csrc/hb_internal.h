@@ -91,6 +91,27 @@ struct hb_ctx {
   float rope_base = 0.f;
 };
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may begin while the
+// kernel in front of it on the stream is still running, and must execute `griddepcontrol.wait`
+// before its first access to memory (the wait returns when that kernel has completed and its
+// writes are visible).  What is gained is the launch latency between two dependent kernels, which
+// dominates a step made of kernels of a few microseconds.
+template <typename... KArgs, typename... Args>
+inline cudaError_t hb_launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                       Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 hb_status hb_fail(hb_ctx* ctx, hb_status code, const char* fmt, ...);
 hb_status hb_check_cuda(hb_ctx* ctx, cudaError_t e, const char* what);
 #define HB_CUDA(ctx, call)                                        \
@@ -125,6 +146,7 @@ struct hb_gemm_args {
   int epilogue;
   const void* residual;
   int64_t ldr;
+  int b_is_weights;        // HB_MATMUL_WEIGHTS_B: nothing in flight writes B
   // rows of A published block by block while the kernel runs (see hb_matmul_gathered)
   const uint32_t* ready;
   uint32_t ready_epoch, ready_spin;

@@ -267,7 +267,8 @@ static hb_status decode_matmul(hb_ctx* ctx, const hb_tensor* A, const hb_tensor*
   if (A->dtype != HB_BF16 && A->dtype != HB_F32)
     return hb_fail(ctx, HB_ERR_UNSUPPORTED, "matmul: dtype %d is not supported", A->dtype);
   const int64_t M = A->shape[0], K = A->shape[1], N = B->shape[1];
-  const int epi = opts ? opts->epilogue : HB_EPI_NONE;
+  const int epi = opts ? (opts->epilogue & 0xff) : HB_EPI_NONE;
+  const bool weights_b = opts && (opts->epilogue & HB_MATMUL_WEIGHTS_B);
   if (epi < HB_EPI_NONE || epi > HB_EPI_RESIDUAL)
     return hb_fail(ctx, HB_ERR_INVALID, "matmul: unknown epilogue %d", epi);
   const int64_t NC = (epi == HB_EPI_SWIGLU) ? N / 2 : N;
@@ -294,6 +295,7 @@ static hb_status decode_matmul(hb_ctx* ctx, const hb_tensor* A, const hb_tensor*
   else if (B->stride[1] == 1 && B->stride[0] >= N) { g->b_mn_major = 1; g->ldb = B->stride[0]; }
   else return hb_fail(ctx, HB_ERR_UNSUPPORTED, "matmul: B must be contiguous along K or along N");
   g->epilogue = epi;
+  g->b_is_weights = weights_b ? 1 : 0;
   if (epi == HB_EPI_RESIDUAL) {
     if (!opts->residual) return hb_fail(ctx, HB_ERR_INVALID, "matmul: residual epilogue without a residual");
     g->residual = opts->residual;

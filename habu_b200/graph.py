@@ -62,10 +62,12 @@ class Graph:
         self.ctx._check(_lib.hb_graph_add(self._h, C.byref(n)))
         return out
 
-    def matmul(self, a, b, out, epilogue=_capi.HB_EPI_NONE, residual=None, config_id=-1, gathered=False):
+    def matmul(self, a, b, out, epilogue=_capi.HB_EPI_NONE, residual=None, config_id=-1, gathered=False, weights=False):
         """gathered=True: `a` is the output of the all_reduce_norm node added just before; the
-        product waits for its rows block by block instead of for the end of the collective."""
-        return self._add(NODE_MATMUL, [a, b, residual], out, [epilogue, config_id, int(gathered)])
+        product waits for its rows block by block instead of for the end of the collective.
+        weights=True: `b` is a weight matrix that no node of the graph writes."""
+        return self._add(NODE_MATMUL, [a, b, residual], out,
+                         [epilogue | (_capi.HB_MATMUL_WEIGHTS_B if weights else 0), config_id, int(gathered)])
 
     def attention(self, q, k, v, out, causal=True, scale=None, lse=None):
         if scale is None:

@@ -165,13 +165,15 @@ class Context:
 
     # -- matmul node --------------------------------------------------------------
     def matmul(self, A: Tensor, B: Tensor, out: Optional[Tensor] = None, epilogue: int = HB_EPI_NONE,
-               residual: Optional[Tensor] = None, config_id: int = -1) -> Tensor:
-        """out[M,N] = epilogue(A[M,K] @ B[K,N]); layouts are read from the strides."""
+               residual: Optional[Tensor] = None, config_id: int = -1, weights: bool = False) -> Tensor:
+        """out[M,N] = epilogue(A[M,K] @ B[K,N]); layouts are read from the strides.  `weights`:
+        B is a weight matrix that nothing in flight writes (lets the M <= 64 kernel stream it in
+        while the kernel in front is still running)."""
         M, N = A.shape[0], B.shape[1]
         if out is None:
             out = self.empty((M, N // 2 if epilogue == HB_EPI_SWIGLU else N), A.dtype)
-        opts = _capi.hb_matmul_opts(epilogue, config_id, residual.ptr if residual else None,
-                                    residual.stride[0] if residual else 0)
+        opts = _capi.hb_matmul_opts(epilogue | (_capi.HB_MATMUL_WEIGHTS_B if weights else 0), config_id,
+                                    residual.ptr if residual else None, residual.stride[0] if residual else 0)
         ta, tb, tc = A.c(), B.c(), out.c()
         self._check(_lib.hb_matmul(self._h, C.byref(ta), C.byref(tb), C.byref(tc), C.byref(opts)))
         return out

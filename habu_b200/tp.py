@@ -332,12 +332,12 @@ class DecodeGraph:
             else:
                 g.rmsnorm(pending, w["g1"], h, residual=xres, eps=cfg.eps)
             qkv = g.temp((B, W))
-            g.matmul(h, w["wqkv"], qkv)
+            g.matmul(h, w["wqkv"], qkv, weights=True)
             g.rope_append(qkv, pos, kv, Hq, Hkv, cfg.rope_base)
             attn = g.temp((B, Hq * hd))
             g.attention_decode(qkv, kv, pos, attn, Hq, Hkv, len_hint=len_hint)
             ao = g.temp((B, d))
-            g.matmul(attn, w["wo"], ao)
+            g.matmul(attn, w["wo"], ao, weights=True)
             h2 = g.temp((B, d))
             if li == 0:
                 g.add(x_in, ao, xres)
@@ -345,11 +345,11 @@ class DecodeGraph:
             else:
                 g.rmsnorm(ao, w["g2"], h2, residual=xres, eps=cfg.eps)
             gu = g.temp((B, 2 * F))
-            g.matmul(h2, w["wgu"], gu)
+            g.matmul(h2, w["wgu"], gu, weights=True)
             act = g.temp((B, F))
             g.swiglu(gu, act)
             fo = g.temp((B, d))
-            g.matmul(act, w["wd"], fo)
+            g.matmul(act, w["wd"], fo, weights=True)
             pending = fo
         g.add(xres, pending, out)
         if advance:

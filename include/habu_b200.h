@@ -87,8 +87,14 @@ enum {
   HB_EPI_SWIGLU = 2,        /* B's N columns interleave (gate,up); C has N/2 columns */
   HB_EPI_RESIDUAL = 3       /* C = A.B + R, R row-major bf16 shaped like C */
 };
+/* OR-ed into hb_matmul_opts.epilogue: B is a weight matrix -- nothing still in flight on the GPU
+ * writes it.  The stream-K kernel (M <= 64) may then start streaming B in while the kernel in
+ * front of it on the stream is still running (programmatic dependent launch); A, C and the
+ * scratch are touched only after that kernel has finished.  Without the flag the launch keeps
+ * plain stream order. */
+#define HB_MATMUL_WEIGHTS_B 0x100
 typedef struct hb_matmul_opts {
-  int32_t epilogue;         /* HB_EPI_* */
+  int32_t epilogue;         /* HB_EPI_*, optionally | HB_MATMUL_WEIGHTS_B */
   int32_t config_id;        /* -1: use the autotune cache / heuristic */
   const void* residual;     /* device pointer, HB_EPI_RESIDUAL only */
   int64_t residual_ld;      /* elements */

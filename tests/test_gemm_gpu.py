@@ -185,3 +185,25 @@ def test_comm_configure_validates_its_arguments(ctx):
         with pytest.raises(hb.HabuError) as e:
             ctx.comm_configure(*bad)
         assert e.value.status == 1
+
+
+def test_weight_matrix_promise_changes_the_launch_not_the_result(ctx):
+    """HB_MATMUL_WEIGHTS_B lets the M <= 64 kernel stream B in before the kernel in front of it on
+    the stream has finished; a chain of such products (each reading the previous one's output as
+    its A, the situation of a generation step) must give the bits of the plainly ordered chain."""
+    M, K = 16, 1024
+    A, Ab = bf16_normal((M, K), SEED + 910, K ** -0.5)
+    Ws = [bf16_normal((K, K), SEED + 911 + i, K ** -0.5) for i in range(4)]
+    dWs = [ctx.upload(wb) for _, wb in Ws]
+    outs = []
+    for weights in (False, True):
+        x = ctx.upload(Ab)
+        for dW in dWs * 3:                      # twelve dependent products back to back
+            x = ctx.matmul(x, dW.T, weights=weights)
+        ctx.sync()
+        outs.append(ctx.download(x))
+    assert np.array_equal(outs[0], outs[1])
+    ref = A
+    for W, _ in Ws * 3:
+        ref = oracle.round_bf16(oracle.gemm(ref, W.T))
+    assert bf16_close(oracle.from_bf16_bits(outs[1]), ref) < 0
