@@ -309,7 +309,8 @@ class DecoderWorkload:
                 cands = [cands[int(os.environ["HB_DECODER_SCHEDULE"])]]
         graphs = []
         for c in cands:
-            graphs.append(DecoderGraph(ctx, cfg, world, rank, layers, HB_AR_AUTO, share=graphs[0] if graphs else None, **c))
+            graphs.append(DecoderGraph(ctx, cfg, world, rank, layers, share=graphs[0] if graphs else None,
+                                       **{"algo": HB_AR_AUTO, **c}))
         sym = max(g.plan()[1] for g in graphs)
         if world > 1:
             ids = [ctx.comm_unique_id() if rank == 0 else None]

@@ -104,7 +104,9 @@ class DecoderGraph:
         self._out_id = None
         self.fused_form, self.fused_ctas, self._share = fused_form, fused_ctas, share
         self.schedule = {"chunks": chunks, "fused": bool(fused and world > 1), "gathered": bool(gathered and world > 1),
-                         "fused_form": fused_form, "fused_ctas": fused_ctas}
+                         "fused_form": fused_form, "fused_ctas": fused_ctas,
+                         "collective": {_capi.HB_AR_AUTO: "auto", _capi.HB_AR_NCCL: "nccl", _capi.HB_AR_P2P: "p2p",
+                                        _capi.HB_AR_NVLS: "nvls"}.get(algo, str(algo))}
         if fused and world > 1:
             self._build_fused(ctx, cfg, world, rank, layers, algo, chunks, gathered)
             return
@@ -214,14 +216,27 @@ class DecoderGraph:
         ao, h2, fo, nxt = (g.temp((T, d), symmetric=True) for _ in range(4))
         for li, w in enumerate(ws):
             qkv = g.temp((T, W))
+            attn = g.temp((T, ql * hd))
+            # When a row block is a whole number of sequences, its QKV product, RoPE and attention
+            # form a chain of their own: block 0's chain runs while the previous layer's last
+            # collective is still gathering block 1.  Otherwise RoPE and attention take all rows.
+            per_block = chunks > 1 and Tc % cfg.seq == 0
             for c in range(chunks):                 # block c starts as soon as its gathered rows have landed
                 g.matmul(rows(h, c, d), w["wqkv"], rows(qkv, c, W), gathered=gathered and li > 0)
-            g.rope(g.view(qkv, 0, (T, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
-            g.rope(g.view(qkv, ql * hd, (T, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
-            v4 = lambda off, H: g.view(qkv, off, (cfg.batch, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
-            attn = g.temp((T, ql * hd))
-            g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
-                        g.view(attn, 0, (cfg.batch, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)), causal=True)
+                if per_block:
+                    r0, Bc = c * Tc, Tc // cfg.seq
+                    g.rope(g.view(qkv, r0 * W, (Tc, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
+                    g.rope(g.view(qkv, r0 * W + ql * hd, (Tc, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
+                    v4 = lambda off, H: g.view(qkv, r0 * W + off, (Bc, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
+                    g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
+                                g.view(attn, r0 * ql * hd, (Bc, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)),
+                                causal=True)
+            if not per_block:
+                g.rope(g.view(qkv, 0, (T, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
+                g.rope(g.view(qkv, ql * hd, (T, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
+                v4 = lambda off, H: g.view(qkv, off, (cfg.batch, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
+                g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
+                            g.view(attn, 0, (cfg.batch, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)), causal=True)
             xin = x0 if li == 0 else x
             for c in range(chunks):
                 g.matmul(rows(attn, c, ql * hd), w["wo"], rows(ao, c, d))
@@ -276,6 +291,9 @@ def candidate_schedules(world: int, gathered: bool = False):
            dict(chunks=2, fused=True, fused_form=2, fused_ctas=64),
            dict(chunks=2, fused=True, fused_form=2, fused_ctas=128),
            dict(chunks=2, fused=True, fused_form=1)]
+    # (Plain peer loads and stores instead of the in-switch reduction move fewer bytes per link on
+    # two ranks -- 153 against 203 us for one exchange -- but the whole step was not faster with
+    # them: 3.41 against 3.35 ms; pass algo=HB_AR_P2P to DecoderGraph to use them.)
     if gathered:
         out += [dict(chunks=1, fused=True, gathered=True, fused_form=2, fused_ctas=128),
                 dict(chunks=1, fused=True, gathered=True, fused_form=2, fused_ctas=64)]
