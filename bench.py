@@ -316,7 +316,11 @@ class DecoderWorkload:
             ids = [ctx.comm_unique_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             ctx.comm_init_rank(world, rank, ids[0])
-            _, self.comm = attach_symmetric(ctx, rank, world, dist, sym)
+            # room behind the graphs' exchange buffers for timing the fused collective alone
+            T_, d_ = cfg.tokens, cfg.d_model
+            sym256 = (sym + 255) // 256 * 256
+            base, self.comm = attach_symmetric(ctx, rank, world, dist, sym256 + 2 * T_ * d_ * 2)
+            self.coll_bufs = (base + sym256, base + sym256 + T_ * d_ * 2)
             for g in graphs:
                 g.plan()
         x0 = oracle.to_bf16_bits(decoder.make_input(cfg))
@@ -396,6 +400,51 @@ class DecoderWorkload:
         return {"per_kind_us": {k: {"nodes": n, "us": round(t, 1)} for k, (n, t) in kinds.items()},
                 "serial_sum_us": round(float(acc.sum()), 1), "nodes": len(lines),
                 "per_node_us": [[l.split()[1], round(float(t), 1)] for l, t in zip(lines, acc)]}
+
+    def collective_times(self, ctx, dist, reps=10):
+        """The fused collective alone (reduce-scatter + residual + RMSNorm + all-gather of one
+        [tokens, d_model] tensor), microseconds per call, in its kernel forms: CUDA events on the
+        context's stream, maximum over ranks.  Every rank must call it."""
+        import ctypes as C
+        import torch
+        from habu_b200 import HB_AR_AUTO, model_ir
+        cfg, lib = self.cfg, model_ir._lib
+        T, d = cfg.tokens, cfg.d_model
+        partial, out = self.coll_bufs
+        res_in, res_out = ctx.empty((T, d)), ctx.empty((T, d))
+        gain = self.dg.weights[0]["g1"]
+        zero = np.zeros((T, d), np.uint16)
+        for ptr in (partial, res_in.ptr):
+            ctx._check(lib.hb_upload(ctx._h, C.c_void_p(ptr), zero.ctypes.data_as(C.c_void_p), zero.nbytes))
+        ctx.sync()
+        stream = self.torch_stream
+        res = {}
+        for name, form, ctas in (("cta_per_row", 1, 0), ("warp_per_row_128", 2, 128), ("warp_per_row_64", 2, 64)):
+            ctx.comm_configure(form, ctas)
+            call = lambda: ctx._check(lib.hb_all_reduce_norm(ctx._h, C.c_void_p(partial), C.c_void_p(gain.ptr),
+                                                             C.c_void_p(res_in.ptr), C.c_void_p(res_out.ptr),
+                                                             C.c_void_p(out), T, d, cfg.eps, 0, HB_AR_AUTO))
+            for _ in range(3):
+                call()
+            ctx.sync()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                call()
+            e1.record(stream)
+            ctx.sync()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / reps * 1e3], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            res[name] = round(float(t.item()), 1)
+        ctx.comm_configure(self.dg.fused_form, self.dg.fused_ctas)
+        ctx.free(res_in)
+        ctx.free(res_out)
+        res["bytes"] = T * d * 2
+        res["collective"] = self.comm
+        return res
 
     def cpu_sample(self):
         """Bounded CPU sample: the same block at batch 1 x seq 256 on the oracle (fp32)."""
@@ -886,6 +935,12 @@ def main():
         if args.node_times and hasattr(wl, "node_times"):
             barrier()
             res["node_times"] = wl.node_times(ctx)
+            if world > 1 and hasattr(wl, "collective_times"):
+                barrier()
+                try:
+                    res["node_times"]["fused_collective_alone_us"] = wl.collective_times(ctx, dist)
+                except Exception as e:      # a diagnostic leg: its failure must not cost the measured line
+                    res["node_times"]["fused_collective_alone_us"] = {"error": str(e)[:300]}
         # correctness of what was just timed, outside the timed region
         if hasattr(wl, "parity"):
             barrier()
