@@ -32,6 +32,11 @@ constexpr int RMS_MAX_VEC = 8;   // cols <= 256 * 8 * 8 = 16384
 // weights in before its own wait) start early.
 #define HB_LAUNCH_DEPENDENTS() asm volatile("griddepcontrol.wait;\n\tgriddepcontrol.launch_dependents;" ::: "memory")
 
+// VEC = 16-byte vectors per thread (cols <= 256 * 8 * VEC).  The row lives in registers, so the
+// instantiation is chosen by the row length: a 4096-wide row needs 16 values per thread, not
+// the 64 of the widest case, and four times as many CTAs fit on an SM (the kernel is bound by
+// the bytes it has in flight).  The order of the arithmetic does not depend on VEC.
+template <int VEC>
 __global__ void __launch_bounds__(RMS_THREADS)
 rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain, uint4* __restrict__ y,
                uint4* residual, int cols8, float inv_cols, float eps) {
@@ -40,10 +45,10 @@ rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain, uint
   const int64_t row = blockIdx.x;
   const uint4* xr = x + row * cols8;
   uint4* rr = residual ? residual + row * cols8 : nullptr;
-  float v[RMS_MAX_VEC][8];
+  float v[VEC][8];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < RMS_MAX_VEC; ++i) {
+  for (int i = 0; i < VEC; ++i) {
     const int c = threadIdx.x + i * RMS_THREADS;
     if (c < cols8) {
       const uint4 a = xr[c];
@@ -75,7 +80,7 @@ rmsnorm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gain, uint
   const float inv = rsqrtf(tot * inv_cols + eps);
   uint4* yr = y + row * cols8;
 #pragma unroll
-  for (int i = 0; i < RMS_MAX_VEC; ++i) {
+  for (int i = 0; i < VEC; ++i) {
     const int c = threadIdx.x + i * RMS_THREADS;
     if (c < cols8) {
       const uint4 g = __ldg(gain + c);
@@ -265,9 +270,16 @@ extern "C" hb_status hb_rmsnorm(hb_ctx* ctx, const void* x, const void* gain, vo
   if (!HB_ALIGNED16(x) || !HB_ALIGNED16(gain) || !HB_ALIGNED16(y) || !HB_ALIGNED16(residual_inout))
     return hb_fail(ctx, HB_ERR_INVALID, "rmsnorm: pointers must be 16-byte aligned");
   if (rows > INT32_MAX) return hb_fail(ctx, HB_ERR_UNSUPPORTED, "rmsnorm: too many rows");
-  hb_launch_dependent(rmsnorm_kernel, dim3((unsigned)rows), dim3(RMS_THREADS), 0, ctx->stream,
-      static_cast<const uint4*>(x), static_cast<const uint4*>(gain), static_cast<uint4*>(y),
-      static_cast<uint4*>(residual_inout), (int)(cols / 8), 1.0f / (float)cols, eps);
+  const int vec = (int)((cols / 8 + RMS_THREADS - 1) / RMS_THREADS);
+#define HB_RMS_LAUNCH(V)                                                                                  \
+  hb_launch_dependent(rmsnorm_kernel<V>, dim3((unsigned)rows), dim3(RMS_THREADS), 0, ctx->stream,       \
+                      static_cast<const uint4*>(x), static_cast<const uint4*>(gain), static_cast<uint4*>(y), \
+                      static_cast<uint4*>(residual_inout), (int)(cols / 8), 1.0f / (float)cols, eps)
+  if (vec <= 1) HB_RMS_LAUNCH(1);
+  else if (vec <= 2) HB_RMS_LAUNCH(2);
+  else if (vec <= 4) HB_RMS_LAUNCH(4);
+  else HB_RMS_LAUNCH(RMS_MAX_VEC);
+#undef HB_RMS_LAUNCH
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "rmsnorm launch");
 }

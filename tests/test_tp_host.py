@@ -74,3 +74,19 @@ def _cpu_rank(rank, world):
 
 def test_two_cpu_ranks_over_gloo_match_the_unsharded_oracle():
     run_ranks(_cpu_rank, 2, timeout=240)
+
+
+def test_candidate_schedules_are_well_formed():
+    """The schedules the bench times: one rank needs none of the collective machinery; several
+    ranks get the exposed schedule first (the safe fallback), the pipelined ones after it, and the
+    gathered-product ones only on request."""
+    from habu_b200.tp import candidate_schedules
+    assert candidate_schedules(1) == [dict(chunks=1, fused=False)]
+    for world in (2, 4, 8):
+        c = candidate_schedules(world)
+        assert c[0] == dict(chunks=1, fused=True, fused_form=1)
+        assert all(s["fused"] and not s.get("gathered") for s in c)
+        assert any(s["chunks"] == 2 and s["fused_form"] == 2 for s in c)
+        g = candidate_schedules(world, gathered=True)
+        assert g[:len(c)] == c and all(s["gathered"] and s["chunks"] == 1 and s["fused_form"] == 2 for s in g[len(c):])
+        assert len(g) > len(c)
