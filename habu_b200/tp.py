@@ -221,9 +221,17 @@ class DecoderGraph:
             # form a chain of their own: block 0's chain runs while the previous layer's last
             # collective is still gathering block 1.  Otherwise RoPE and attention take all rows.
             per_block = chunks > 1 and Tc % cfg.seq == 0
+            xin = x0 if li == 0 else x
+
+            def attention_out(c):
+                g.matmul(rows(attn, c, ql * hd), w["wo"], rows(ao, c, d))
+                g.all_reduce_norm(rows(ao, c, d), w["g2"], rows(xin, c, d), rows(x, c, d), rows(h2, c, d), eps=cfg.eps,
+                                  algo=algo, stream=side, ready_words=gathered)
             for c in range(chunks):                 # block c starts as soon as its gathered rows have landed
                 g.matmul(rows(h, c, d), w["wqkv"], rows(qkv, c, W), gathered=gathered and li > 0)
                 if per_block:
+                    # the whole attention sublayer of block c, so that its collective runs under the
+                    # QKV product, RoPE, attention and output product of block c+1
                     r0, Bc = c * Tc, Tc // cfg.seq
                     g.rope(g.view(qkv, r0 * W, (Tc, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
                     g.rope(g.view(qkv, r0 * W + ql * hd, (Tc, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
@@ -231,17 +239,15 @@ class DecoderGraph:
                     g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
                                 g.view(attn, r0 * ql * hd, (Bc, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)),
                                 causal=True)
+                    attention_out(c)
             if not per_block:
                 g.rope(g.view(qkv, 0, (T, ql * hd), (W, 1)), cfg.seq, ql, hd, cfg.rope_base)
                 g.rope(g.view(qkv, ql * hd, (T, kl * hd), (W, 1)), cfg.seq, kl, hd, cfg.rope_base)
                 v4 = lambda off, H: g.view(qkv, off, (cfg.batch, cfg.seq, H, hd), (cfg.seq * W, W, hd, 1))
                 g.attention(v4(0, ql), v4(ql * hd, kl), v4((ql + kl) * hd, kl),
                             g.view(attn, 0, (cfg.batch, cfg.seq, ql, hd), (cfg.seq * ql * hd, ql * hd, hd, 1)), causal=True)
-            xin = x0 if li == 0 else x
-            for c in range(chunks):
-                g.matmul(rows(attn, c, ql * hd), w["wo"], rows(ao, c, d))
-                g.all_reduce_norm(rows(ao, c, d), w["g2"], rows(xin, c, d), rows(x, c, d), rows(h2, c, d), eps=cfg.eps,
-                                  algo=algo, stream=side, ready_words=gathered)
+                for c in range(chunks):
+                    attention_out(c)
             act = g.temp((T, fl))
             last = li + 1 == len(ws)
             for c in range(chunks):
