@@ -827,13 +827,23 @@ def main():
     stream = torch.cuda.Stream()
     pk = peaks()
 
+    # Pinned buffers of the end-to-end leg go to the memory node of this rank's GPU where the
+    # kernel allows it: every rank starts on the same cores, and eight ranks' buffers on one
+    # memory controller make the copies of the other socket's GPUs cross the interconnect.
+    from habu_b200.hostmem import near_gpu
+    props = torch.cuda.get_device_properties(local_rank)
+    bus_id = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+
     def pinned(a: np.ndarray) -> np.ndarray:
-        t = torch.empty(a.shape, dtype={2: torch.int16, 4: torch.float32}[a.dtype.itemsize]).pin_memory()
-        out = t.numpy().view(a.dtype)
-        out[...] = a
+        with near_gpu(bus_id) as place:
+            t = torch.empty(a.shape, dtype={2: torch.int16, 4: torch.float32}[a.dtype.itemsize]).pin_memory()
+            out = t.numpy().view(a.dtype)
+            out[...] = a
+        pinned.placement = {"gpu_node": place.node, "policy": place.outcome}
         pinned.keep.append(t)
         return out
     pinned.keep = []
+    pinned.placement = None
 
     def measure(name, steps, warmup, full):
         """Times one workload.  full=False: device-resident leg and parity check only."""
@@ -931,7 +941,8 @@ def main():
             e2e_ms = timed(wl.step_e2e, e2e_steps) / e2e_steps
             e2e_value = wl.value(e2e_ms, world) if own_value else wl.flop * world / (e2e_ms * 1e-3) / 1e12
             res["e2e"] = {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
-                          "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms}
+                          "d2h_bytes_per_step": wl.d2h, "ms_per_step": e2e_ms,
+                          "host_buffers": pinned.placement}
         if args.node_times and hasattr(wl, "node_times"):
             barrier()
             res["node_times"] = wl.node_times(ctx)

@@ -67,3 +67,30 @@ def test_static_entry_points_refuse_a_device_that_is_not_current():
     assert lib.hb_static_status(63, words) == 1
     assert b"current CUDA device" in lib.hb_static_last_error()
     assert lib.hb_static_status(-1, words) == 1
+
+
+def test_host_buffer_placement_helpers(tmp_path):
+    """sysfs parsing of the pinned-buffer placement helper, against a fake sysfs tree."""
+    from habu_b200 import hostmem
+    assert hostmem.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert hostmem.parse_cpulist("") == []
+    assert hostmem.normalise_bus_id("00000000:1B:00.0") == "0000:1b:00.0"
+    assert hostmem.normalise_bus_id("1b:00.0") == "0000:1b:00.0"
+    dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node"
+    node.mkdir(parents=True)
+    (node / "online").write_text("0-1\n")
+    assert hostmem.gpu_numa_node("0000:1B:00.0", str(tmp_path)) == 1
+    assert hostmem.gpu_numa_node("0000:1c:00.0", str(tmp_path)) is None
+    (dev / "numa_node").write_text("-1\n")
+    assert hostmem.gpu_numa_node("0000:1b:00.0", str(tmp_path)) is None
+    assert hostmem.online_nodes(str(tmp_path)) == [0, 1]
+    # no answer from sysfs: the block runs unchanged and says so
+    with hostmem.near_gpu("0000:1b:00.0", str(tmp_path)) as place:
+        pass
+    assert place.outcome.startswith("unchanged")
+    with hostmem.near_gpu(None) as place:
+        pass
+    assert place.outcome.startswith("unchanged")
