@@ -119,7 +119,7 @@ def test_bf16_linearity_property_full_size(ctx):
 
 
 def test_host_entry_point_pipelines_row_chunks(ctx):
-    # M >= 2048 goes through the host call as four row chunks over the copy-in, compute and
+    # M >= 2048 goes through the host call as four to eight row chunks over the copy-in, compute and
     # copy-out streams; two calls in a row reuse the staging buffer and the events
     M, N, K = 2048, 264, 136
     A, Ab = bf16_normal((M, K), SEED + 15, K ** -0.5)
