@@ -94,3 +94,26 @@ def test_host_buffer_placement_helpers(tmp_path):
     with hostmem.near_gpu(None) as place:
         pass
     assert place.outcome.startswith("unchanged")
+
+
+def test_host_buffer_placement_sets_and_restores_policy(tmp_path, monkeypatch):
+    """With a GPU on node 1 of a two-node box the block asks for MPOL_PREFERRED on node 1 and
+    puts the default policy back on exit; a refused call leaves everything unchanged."""
+    from habu_b200 import hostmem
+    dev = tmp_path / "bus/pci/devices/0000:9a:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node"
+    node.mkdir(parents=True)
+    (node / "online").write_text("0-1\n")
+    calls = []
+    monkeypatch.setattr(hostmem, "_set_mempolicy", lambda mode, n: calls.append((mode, n)) or 0)
+    with hostmem.near_gpu("0000:9A:00.0", str(tmp_path)) as place:
+        assert calls == [(hostmem._MPOL_PREFERRED, 1)]
+    assert place.outcome == "preferred" and place.node == 1
+    assert calls[-1] == (hostmem._MPOL_DEFAULT, None)
+    calls.clear()
+    monkeypatch.setattr(hostmem, "_set_mempolicy", lambda mode, n: calls.append((mode, n)) or -1)
+    with hostmem.near_gpu("0000:9a:00.0", str(tmp_path)) as place:
+        pass
+    assert place.outcome.startswith("unchanged: set_mempolicy refused") and len(calls) == 1
