@@ -46,7 +46,14 @@ struct GemmParams {
   uint32_t ready_spin;      // polls before the wait gives up
   int ready_rows;           // rows per word
   int perm_world, perm_rank;  // > 1: M-tiles are visited owner by owner in turn, this rank's rows first
+  int tma_store;            // the epilogue stages 32 x 32 blocks in shared memory and stores them with TMA
 };
+
+// Output staging: each of the four epilogue warps owns two buffers of 32 rows x 32 bf16 columns
+// (64-byte rows, 64-byte swizzle: the 16-byte piece c of row r sits at piece c ^ ((r >> 1) & 3),
+// so that the row-per-lane writes of a warp spread over all banks).
+constexpr int STAGE_BUF_BYTES = 32 * 64;
+constexpr int STAGE_BYTES = 4 * 2 * STAGE_BUF_BYTES;
 
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
   uint32_t v;
@@ -91,7 +98,8 @@ struct SmemLayout {
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int OFF_TMEM_PTR = OFF_BAR + NUM_BARS * 8;
   static constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
-  static constexpr int TOTAL = OFF_ABORT + 4;
+  static constexpr int OFF_STAGE = (OFF_ABORT + 4 + 1023) & ~1023;   // output staging of the epilogue warps
+  static constexpr int TOTAL = OFF_STAGE + STAGE_BYTES;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
 };
 
@@ -188,10 +196,99 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, bool vec_ok,
     }
 }
 
+// The same 32-column chunk through shared memory: every lane applies the epilogue to its row
+// and writes the 64 bytes into the warp's staging buffer; lane 0 then hands the 32 x 32 block
+// to TMA, which writes full lines (a warp's own stores touch 32 different rows with 16 bytes
+// each) and clips the block at the matrix edge.  `row0` is the first of the warp's 32 rows, `c`
+// the running number of the chunk over all tiles of this warp (a tile has an even number of
+// chunks), `stage` the warp's two buffers, used in turn.  With the SwiGLU epilogue a chunk yields
+// 16 output columns, so two consecutive chunks fill one block.
+__device__ __forceinline__ void epilogue_chunk_staged(const GemmParams& p, const CUtensorMap* tmC, uint32_t stage,
+                                                      int lane, int row0, int col0, int c, const uint32_t (&v)[32]) {
+  if (p.epilogue == HB_EPI_SWIGLU) {
+    stage += ((c >> 1) & 1) * STAGE_BUF_BYTES;
+    const int odd = c & 1;
+    if (!odd) {
+      if (lane == 0) tma_store_wait_read<1>();
+      __syncwarp();
+    }
+    if (row0 < p.M && col0 < p.N) {
+      const uint32_t mine = stage + lane * 64;
+      const int sw = (lane >> 1) & 3;
+      uint32_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g0 = __uint_as_float(v[4 * j]), u0 = __uint_as_float(v[4 * j + 1]);
+        const float g1 = __uint_as_float(v[4 * j + 2]), u1 = __uint_as_float(v[4 * j + 3]);
+        o[j] = pack_bf16x2(silu(g0) * u0, silu(g1) * u1);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(mine + (((odd * 2 + h) ^ sw) << 4)),
+                     "r"(o[4 * h]), "r"(o[4 * h + 1]), "r"(o[4 * h + 2]), "r"(o[4 * h + 3])
+                     : "memory");
+    }
+    if (odd) {
+      if (row0 < p.M && col0 - 32 < p.N) {     // the pair's first chunk was inside the matrix
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) tma_store_2d(tmC, stage, (col0 - 32) >> 1, row0);
+      }
+      if (lane == 0) tma_store_commit();
+    }
+    return;
+  }
+  stage += (c & 1) * STAGE_BUF_BYTES;
+  if (lane == 0) tma_store_wait_read<1>();     // the store issued two chunks ago has read this buffer
+  __syncwarp();
+  if (row0 < p.M && col0 < p.N) {
+    const int row = row0 + lane;
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+    if (p.epilogue == HB_EPI_GELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+    } else if (p.epilogue == HB_EPI_RESIDUAL && row < p.M) {
+      const __nv_bfloat16* r = p.R + static_cast<int64_t>(row) * p.ldr + col0;
+      if (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0) && col0 + 32 <= p.N) {
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const uint4 rv = __ldg(reinterpret_cast<const uint4*>(r) + j4);
+          const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 rf = __bfloat1622float2(r2[j]);
+            f[j4 * 8 + 2 * j] += rf.x;
+            f[j4 * 8 + 2 * j + 1] += rf.y;
+          }
+        }
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) f[j] += __bfloat162float(r[j]);
+      }
+    }
+    const uint32_t mine = stage + lane * 64;
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t o0 = pack_bf16x2(f[8 * c], f[8 * c + 1]), o1 = pack_bf16x2(f[8 * c + 2], f[8 * c + 3]);
+      const uint32_t o2 = pack_bf16x2(f[8 * c + 4], f[8 * c + 5]), o3 = pack_bf16x2(f[8 * c + 6], f[8 * c + 7]);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(mine + ((c ^ sw) << 4)), "r"(o0), "r"(o1),
+                   "r"(o2), "r"(o3)
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) tma_store_2d(tmC, stage, col0, row0);
+  }
+  if (lane == 0) tma_store_commit();           // one group per chunk, empty or not: keeps the count uniform
+}
+
 template <int BN, int STAGES, int KPS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using L = SmemLayout<BN, STAGES, KPS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -327,6 +424,7 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int it = 0;
     bool ok = true;
     const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
+    const uint32_t stage_mine = smem_base + L::OFF_STAGE + q * 2 * STAGE_BUF_BYTES;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
       int tm, tn;
       tile_coords(tile, p, tm, tn);
@@ -342,11 +440,15 @@ hb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_32x32(t_row + c * 32, v);
         tmem_wait_ld();
         const int col0 = tn * BN + c * 32;
-        epilogue_chunk(p, vec_ok, row, col0, v);
+        if (p.tma_store)
+          epilogue_chunk_staged(p, &tmC, stage_mine, lane, tm * BM + q * 32, col0, it * (BN / 32) + c, v);
+        else
+          epilogue_chunk(p, vec_ok, row, col0, v);
       }
       tc_fence_before();
       mbar_arrive(bar_tempty + acc * 8);
     }
+    if (p.tma_store && lane == 0) tma_store_wait<0>();   // the staged blocks have left shared memory and landed
     if (!ok && p.status && lane == 0) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 3; }
   }
 
@@ -390,14 +492,15 @@ struct SmemLayout2 {
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int OFF_TMEM_PTR = OFF_BAR + NUM_BARS * 8;
   static constexpr int OFF_ABORT = OFF_TMEM_PTR + 4;
-  static constexpr int TOTAL = OFF_ABORT + 4;
+  static constexpr int OFF_STAGE = (OFF_ABORT + 4 + 1023) & ~1023;
+  static constexpr int TOTAL = OFF_STAGE + STAGE_BYTES;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
 
 template <int BN2, int STAGES, int KPS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                         const GemmParams p) {
+                         const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using L = SmemLayout2<BN2, STAGES, KPS>;
   constexpr uint32_t TMEM_COLS = 2 * BN2;          // two accumulators: 512 or 256 columns
   extern __shared__ uint8_t smem_raw[];
@@ -535,6 +638,7 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     bool ok = true;
     const bool vec_ok = ((p.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15) == 0);
     const uint32_t tempty_leader = mapa(bar_tempty, 0);
+    const uint32_t stage_mine = smem_base + L::OFF_STAGE + q * 2 * STAGE_BUF_BYTES;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
       int tm, tn;
       tile_coords(tile, p, tm, tn);
@@ -549,11 +653,16 @@ hb_gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         uint32_t v[32];
         tmem_ld_32x32(t_row + c * 32, v);
         tmem_wait_ld();
-        epilogue_chunk(p, vec_ok, row, tn * BN2 + c * 32, v);
+        if (p.tma_store)
+          epilogue_chunk_staged(p, &tmC, stage_mine, lane, tm * 256 + static_cast<int>(cta_rank) * 128 + q * 32,
+                                tn * BN2 + c * 32, it * (BN2 / 32) + c, v);
+        else
+          epilogue_chunk(p, vec_ok, row, tn * BN2 + c * 32, v);
       }
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + acc * 8);
     }
+    if (p.tma_store && lane == 0) tma_store_wait<0>();
     if (!ok && p.status && lane == 0) { atomicCAS(p.status, 0, HB_ERR_TIMEOUT); p.status[1] = HB_KTAG_GEMM; p.status[2] = 13; }
   }
 
@@ -591,7 +700,7 @@ constexpr int kNumRasters = sizeof(kRasters) / sizeof(kRasters[0]);
 constexpr int kNumConfigs = kNumVariants * kNumRasters;   // config_id = variant * kNumRasters + raster index
 
 template <int BN, int STAGES, int KPS>
-hb_status launch_cfg(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p) {
+hb_status launch_cfg(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, GemmParams& p) {
   using L = SmemLayout<BN, STAGES, KPS>;
   static_assert(L::DYN_BYTES <= 227 * 1024, "ring does not fit shared memory");
   auto kern = hb_gemm_bf16_kernel<BN, STAGES, KPS>;
@@ -606,13 +715,13 @@ hb_status launch_cfg(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  kern<<<grid, GEMM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, p);
+  kern<<<grid, GEMM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, tmC, p);
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "gemm launch");
 }
 
 template <int BN2, int STAGES, int KPS>
-hb_status launch_pair(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB, GemmParams& p) {
+hb_status launch_pair(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, GemmParams& p) {
   using L = SmemLayout2<BN2, STAGES, KPS>;
   static_assert(L::DYN_BYTES <= 227 * 1024, "ring does not fit shared memory");
   auto kern = hb_gemm_bf16_pair_kernel<BN2, STAGES, KPS>;
@@ -642,7 +751,7 @@ hb_status launch_pair(hb_ctx* ctx, const CUtensorMap& tmA, const CUtensorMap& tm
   const int tiles = p.tiles_m * p.tiles_n;
   const int max_pairs = resident_pairs[ctx->device & 63];
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
-  kern<<<2 * pairs, GEMM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, p);
+  kern<<<2 * pairs, GEMM_THREADS, L::DYN_BYTES, ctx->stream>>>(tmA, tmB, tmC, p);
   ctx->launches++;
   return hb_check_cuda(ctx, cudaGetLastError(), "pair gemm launch");
 }
@@ -696,7 +805,23 @@ hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id)
                                CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
   if ((st = hb_make_tensor_map(ctx, &tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.B, dimsB, strB, boxB,
                                CU_TENSOR_MAP_SWIZZLE_128B)) != HB_OK) return st;
+  // Output through shared memory and TMA (32 x 32 blocks, 64-byte swizzle) whenever the output's
+  // base and pitch allow a tensor map; otherwise the row-per-lane stores.  HB_GEMM_TMA_STORE=0
+  // keeps the latter.
+  CUtensorMap tmC = tmA;
+  bool tma_store = (a.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(a.C) & 15) == 0;
+  if (tma_store) {
+    if (const char* e = getenv("HB_GEMM_TMA_STORE")) tma_store = atoi(e) != 0;
+  }
+  if (tma_store) {
+    uint64_t dimsC[2] = {(uint64_t)(a.epilogue == HB_EPI_SWIGLU ? a.N / 2 : a.N), (uint64_t)a.M};
+    uint64_t strC[1] = {(uint64_t)a.ldc * 2};
+    uint32_t boxC[2] = {32, 32};
+    if ((st = hb_make_tensor_map(ctx, &tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.C, dimsC, strC, boxC,
+                                 CU_TENSOR_MAP_SWIZZLE_64B)) != HB_OK) return st;
+  }
   GemmParams p;
+  p.tma_store = tma_store ? 1 : 0;
   p.C = static_cast<__nv_bfloat16*>(a.C);
   p.R = static_cast<const __nv_bfloat16*>(a.residual);
   p.M = (int)a.M; p.N = (int)a.N; p.K = (int)a.K;
@@ -712,8 +837,8 @@ hb_status hb_launch_gemm_bf16(hb_ctx* ctx, const hb_gemm_args& a, int config_id)
     const int64_t tiles_m = (a.M + tile_rows - 1) / tile_rows;
     if (a.M % tile_rows == 0 && tiles_m % a.perm_world == 0) { p.perm_world = a.perm_world; p.perm_rank = a.perm_rank; }
   }
-#define HB_CASE1(BN, ST, KP) if (cfg.cluster == 1 && cfg.bn == BN && cfg.stages == ST && cfg.kps == KP) return launch_cfg<BN, ST, KP>(ctx, tmA, tmB, p)
-#define HB_CASE2(BN, ST, KP) if (cfg.cluster == 2 && cfg.bn == BN && cfg.stages == ST && cfg.kps == KP) return launch_pair<BN, ST, KP>(ctx, tmA, tmB, p)
+#define HB_CASE1(BN, ST, KP) if (cfg.cluster == 1 && cfg.bn == BN && cfg.stages == ST && cfg.kps == KP) return launch_cfg<BN, ST, KP>(ctx, tmA, tmB, tmC, p)
+#define HB_CASE2(BN, ST, KP) if (cfg.cluster == 2 && cfg.bn == BN && cfg.stages == ST && cfg.kps == KP) return launch_pair<BN, ST, KP>(ctx, tmA, tmB, tmC, p)
   HB_CASE1(256, 4, 1); HB_CASE1(256, 3, 1); HB_CASE1(256, 2, 2);
   HB_CASE1(128, 6, 1); HB_CASE1(128, 4, 1); HB_CASE1(128, 3, 2);
   HB_CASE1(64, 8, 1);  HB_CASE1(64, 5, 1);  HB_CASE1(64, 4, 2);
