@@ -8,18 +8,21 @@ done in guarded steps, a failure inside a step is recorded rather than raised, a
 every step the ranks agree over the host channel (a gloo group) whether anyone failed.  If
 so, every rank stops issuing collectives, runs the same tear-down (close the context, free
 the symmetric buffer, destroy the process group) and only then re-raises."""
+import datetime
 import multiprocessing as mp
 import os
-import socket
+import tempfile
 import traceback
 
 
-def _free_port():
-    s = socket.socket()
-    s.bind(("127.0.0.1", 0))
-    p = s.getsockname()[1]
-    s.close()
-    return p
+def init_group(backend, rank, world, **kw):
+    """init_process_group over a file store.  A TCP store needs a port that is picked before the
+    ranks start and can be taken by somebody else before rank 0 binds it (seen once: rank 0 died
+    with EADDRINUSE and its peer sat in the rendezvous until the harness gave up); a file needs
+    none.  The short timeout makes a rank whose peer never arrives fail within two minutes."""
+    import torch.distributed as dist
+    dist.init_process_group(backend, init_method="file://" + os.environ["HB_TEST_RDZV_FILE"], rank=rank,
+                            world_size=world, timeout=datetime.timedelta(seconds=120), **kw)
 
 
 class RankGuard:
@@ -56,9 +59,9 @@ class RankGuard:
             raise AssertionError("another rank failed; this rank stopped with it")
 
 
-def _entry(fn, rank, world, port, q, args):
-    os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank),
-                       "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank)})
+def _entry(fn, rank, world, rdzv, q, args):
+    os.environ.update({"HB_TEST_RDZV_FILE": rdzv, "RANK": str(rank), "WORLD_SIZE": str(world),
+                       "LOCAL_RANK": str(rank)})
     try:
         fn(rank, world, *args)
         q.put((rank, None))
@@ -69,8 +72,9 @@ def _entry(fn, rank, world, port, q, args):
 def run_ranks(fn, world, args=(), timeout=300):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(fn, r, world, port, q, args)) for r in range(world)]
+    rdzv_dir = tempfile.mkdtemp(prefix="hb_rdzv_")
+    rdzv = os.path.join(rdzv_dir, "store")
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, rdzv, q, args)) for r in range(world)]
     for p in procs:
         p.start()
     errors = []
@@ -83,16 +87,23 @@ def run_ranks(fn, world, args=(), timeout=300):
                 break
             if err and "another rank failed" not in err:
                 errors.append(f"rank {rank}:\n{err}")
+                timeout = min(timeout, 150)   # its peers follow within the group's own timeout, or never
             elif err:
                 errors.append(f"rank {rank} stopped because a peer failed")
     finally:
         # ranks tear down by themselves; give them time, and end a process only as a last resort
         for p in procs:
-            p.join(timeout=120)
+            p.join(timeout=30 if errors else 120)
         for p in procs:
             if p.is_alive():
                 p.terminate()
                 p.join(timeout=30)
                 if p.is_alive():
                     p.kill()
+    try:
+        if os.path.exists(rdzv):
+            os.unlink(rdzv)
+        os.rmdir(rdzv_dir)
+    except OSError:
+        pass
     assert not errors, "\n".join(errors)

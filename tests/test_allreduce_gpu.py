@@ -19,8 +19,8 @@ def _rank_main(rank, world, algo_name, count, dtype_name):
     import habu_b200 as hb
     import oracle
     from habu_b200 import model_ir
-    from mp_util import RankGuard
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from mp_util import RankGuard, init_group
+    init_group("gloo", rank, world)
     guard = RankGuard()
     ctx = None
     with guard:
@@ -117,9 +117,9 @@ def _nvls_rank(rank, world, count, dtype_name):
     import habu_b200 as hb
     import oracle
     from habu_b200 import model_ir
-    from mp_util import RankGuard
+    from mp_util import RankGuard, init_group
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    init_group("nccl", rank, world, device_id=torch.device("cuda", rank))
     guard = RankGuard(dist.new_group(backend="gloo"))
     ctx = buf = hdl = None
     have_mc = False

@@ -84,9 +84,9 @@ def _tp_rank(rank, world, nvls):
     import torch.distributed as dist
 
     import habu_b200 as hb
-    from mp_util import RankGuard
+    from mp_util import RankGuard, init_group
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    init_group("nccl", rank, world, device_id=torch.device("cuda", rank))
     guard = RankGuard(dist.new_group(backend="gloo"))
     ctx = buf = hdl = None
     outs, graphs = {}, {}

@@ -5,7 +5,7 @@ batch.  The device trainer (`habu_b200.autograd.MlpTrainer`) follows the same co
 this test pins the convention itself with the oracle, no GPU involved."""
 import numpy as np
 
-from mp_util import run_ranks
+from mp_util import init_group, run_ranks
 
 WIDTH, BATCH, LAYERS = 64, 32, 3
 
@@ -16,7 +16,7 @@ def _rank(rank, world):
 
     import oracle
     from oracle import mlp
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    init_group("gloo", rank, world)
     ws = mlp.make_weights(WIDTH, LAYERS)
     wb = [oracle.round_bf16(w.copy()) for w in ws]        # bf16 working copy; round_bf16 works in place
     x, y = mlp.make_batch(BATCH, WIDTH, rank)

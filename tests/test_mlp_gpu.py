@@ -149,8 +149,8 @@ def _dp_rank(rank, world):
 
     import habu_b200 as hb
     from habu_b200.autograd import MlpTrainer
-    from mp_util import RankGuard
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from mp_util import RankGuard, init_group
+    init_group("gloo", rank, world)
     guard = RankGuard()
     ctx = None
     with guard:

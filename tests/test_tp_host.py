@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from habu_b200.tp import DecoderConfig, check_shardable, shard_layer, shard_range
-from mp_util import run_ranks
+from mp_util import init_group, run_ranks
 
 SMALL = DecoderConfig(d_model=128, n_q_heads=4, n_kv_heads=2, head_dim=32, ffn_hidden=256, n_layers=2, batch=2, seq=16)
 
@@ -50,7 +50,7 @@ def _cpu_rank(rank, world):
     import torch
     import torch.distributed as dist
     from oracle import decoder
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    init_group("gloo", rank, world)
     cfg = SMALL
     layers = [decoder.make_layer(cfg, i) for i in range(cfg.n_layers)]
     x0 = decoder.make_input(cfg)
