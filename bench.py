@@ -41,7 +41,7 @@ NVSMI_Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu capture
 # (profiles/), scaled to the full launch; None where not captured.
-NCU_TRAFFIC_BYTES = {"gemm": 1.059352e9 + 127.465216e6, "skinny": 134.590976e6 + 4.355840e6,
+NCU_TRAFFIC_BYTES = {"gemm": 1.078711e9 + 127.863552e6, "skinny": 134.590976e6 + 4.355840e6,
                      "attention": 806.299392e6 + 255.520768e6}
 
 
