@@ -55,12 +55,58 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU during the timed region."""
+    """Samples the SM clock, power and throttle reasons of one GPU during the timed region:
+    through NVML every millisecond where the bindings load (a 15 ms region still gets about ten
+    samples), else one nvidia-smi line every 100 ms.  Read-only either way."""
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, bus_id: str = None):
         self.index, self.rows, self.proc = index, [], None
+        self.bus_id, self.nvml, self.samples, self.stop_flag = bus_id, None, [], False
+
+    def _start_nvml(self) -> bool:
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = (pynvml.nvmlDeviceGetHandleByPciBusId(self.bus_id.encode()) if self.bus_id
+                 else pynvml.nvmlDeviceGetHandleByIndex(self.index))
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)       # fails here rather than in the thread
+        except Exception:
+            return False
+        self.nvml, self.max_mhz = pynvml, mx
+
+        def poll():
+            nv = self.nvml
+            while not self.stop_flag:
+                try:
+                    clk = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                    why = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    mw = nv.nvmlDeviceGetPowerUsage(h)
+                    self.samples.append((clk, why, mw))
+                except Exception:
+                    pass
+                time.sleep(0.001)
+        self.t = threading.Thread(target=poll, daemon=True)
+        self.t.start()
+        return True
+
+    def _stop_nvml(self) -> dict:
+        self.stop_flag = True
+        self.t.join(timeout=2)
+        nv = self.nvml
+        names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        sm = [c for c, _, _ in self.samples]
+        reasons = sorted(n for n, bit in names.items() if any(w & bit for _, w, _ in self.samples))
+        pw = [mw / 1e3 for _, _, mw in self.samples]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": float(self.max_mhz),
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": reasons, "source": "nvml"}
 
     def start(self):
+        if self._start_nvml():
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={NVSMI_Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -75,6 +121,8 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self) -> dict:
+        if self.nvml:
+            return self._stop_nvml()
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -86,7 +134,8 @@ class ClockSampler:
         reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v == "Active"})
         pw = [float(r[3]) for r in self.rows if len(r) >= 9 and r[3].replace(".", "").isdigit()]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": reasons}
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": reasons,
+                "source": "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------- workloads
@@ -896,7 +945,7 @@ def main():
 
         for _ in range(warmup):
             wl.step(ctx)
-        sampler = ClockSampler(local_rank)
+        sampler = ClockSampler(local_rank, bus_id)
         if rank == 0:
             sampler.start()
         l0 = ctx.launches
@@ -925,7 +974,7 @@ def main():
             # the same step back to back for about two seconds: the power-capped regime, against the
             # sustained cuBLAS figure; the clock sampler runs across it
             n = max(steps, int(np.ceil(args.sustained_seconds * 1e3 / ms_per_step)))
-            sampler = ClockSampler(local_rank)
+            sampler = ClockSampler(local_rank, bus_id)
             if rank == 0:
                 sampler.start()
             sus_ms = timed(wl.step, n) / n
