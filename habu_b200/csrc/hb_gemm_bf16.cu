@@ -127,6 +127,46 @@ __device__ __forceinline__ float gelu_erf(float x) {
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
+// SwiGLU of one 32-column accumulator chunk: columns interleave (gate, up), 16 outputs
+// out[j] = silu(acc[2j]) * acc[2j+1], packed in pairs.
+__device__ __forceinline__ void swiglu_chunk(const uint32_t (&v)[32], uint32_t (&o)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float g0 = __uint_as_float(v[4 * j]), u0 = __uint_as_float(v[4 * j + 1]);
+    const float g1 = __uint_as_float(v[4 * j + 2]), u1 = __uint_as_float(v[4 * j + 3]);
+    o[j] = pack_bf16x2(silu(g0) * u0, silu(g1) * u1);
+  }
+}
+
+// The other epilogues of one 32-column chunk of row `row` (none, GELU, + residual), in fp32.
+__device__ __forceinline__ void epilogue_values(const GemmParams& p, int row, int col0, const uint32_t (&v)[32],
+                                                float (&f)[32]) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+  if (p.epilogue == HB_EPI_GELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
+  } else if (p.epilogue == HB_EPI_RESIDUAL && row < p.M) {
+    const __nv_bfloat16* r = p.R + static_cast<int64_t>(row) * p.ldr + col0;
+    if (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0) && col0 + 32 <= p.N) {
+#pragma unroll
+      for (int j4 = 0; j4 < 4; ++j4) {
+        const uint4 rv = __ldg(reinterpret_cast<const uint4*>(r) + j4);
+        const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 rf = __bfloat1622float2(r2[j]);
+          f[j4 * 8 + 2 * j] += rf.x;
+          f[j4 * 8 + 2 * j + 1] += rf.y;
+        }
+      }
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) f[j] += __bfloat162float(r[j]);
+    }
+  }
+}
+
 // One 32-column chunk of one output row: apply the epilogue, round to bf16 once, store.
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, bool vec_ok, int row, int col0,
                                                const uint32_t (&v)[32]) {
@@ -137,12 +177,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, bool vec_ok,
       const int on = p.N >> 1;
       __nv_bfloat16* dst = p.C + static_cast<int64_t>(row) * p.ldc + ocol0;
       uint32_t o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float g0 = __uint_as_float(v[4 * j]), u0 = __uint_as_float(v[4 * j + 1]);
-        const float g1 = __uint_as_float(v[4 * j + 2]), u1 = __uint_as_float(v[4 * j + 3]);
-        o[j] = pack_bf16x2(silu(g0) * u0, silu(g1) * u1);
-      }
+      swiglu_chunk(v, o);
       if (vec_ok && ocol0 + 16 <= on) {
         uint4* d4 = reinterpret_cast<uint4*>(dst);
         d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -154,31 +189,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, bool vec_ok,
       }
     } else {
       float f[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-      if (p.epilogue == HB_EPI_GELU) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
-      } else if (p.epilogue == HB_EPI_RESIDUAL) {
-        const __nv_bfloat16* r = p.R + static_cast<int64_t>(row) * p.ldr + col0;
-        if (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0) &&
-            col0 + 32 <= p.N) {
-#pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4) {
-            const uint4 rv = __ldg(reinterpret_cast<const uint4*>(r) + j4);
-            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 rf = __bfloat1622float2(r2[j]);
-              f[j4 * 8 + 2 * j] += rf.x;
-              f[j4 * 8 + 2 * j + 1] += rf.y;
-            }
-          }
-        } else {
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) f[j] += __bfloat162float(r[j]);
-        }
-      }
+      epilogue_values(p, row, col0, v, f);
       uint32_t o[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) o[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
@@ -216,12 +227,7 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmParams& p, const
       const uint32_t mine = stage + lane * 64;
       const int sw = (lane >> 1) & 3;
       uint32_t o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float g0 = __uint_as_float(v[4 * j]), u0 = __uint_as_float(v[4 * j + 1]);
-        const float g1 = __uint_as_float(v[4 * j + 2]), u1 = __uint_as_float(v[4 * j + 3]);
-        o[j] = pack_bf16x2(silu(g0) * u0, silu(g1) * u1);
-      }
+      swiglu_chunk(v, o);
 #pragma unroll
       for (int h = 0; h < 2; ++h)
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(mine + (((odd * 2 + h) ^ sw) << 4)),
@@ -242,32 +248,8 @@ __device__ __forceinline__ void epilogue_chunk_staged(const GemmParams& p, const
   if (lane == 0) tma_store_wait_read<1>();     // the store issued two chunks ago has read this buffer
   __syncwarp();
   if (row0 < p.M && col0 < p.N) {
-    const int row = row0 + lane;
     float f[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-    if (p.epilogue == HB_EPI_GELU) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) f[j] = gelu_erf(f[j]);
-    } else if (p.epilogue == HB_EPI_RESIDUAL && row < p.M) {
-      const __nv_bfloat16* r = p.R + static_cast<int64_t>(row) * p.ldr + col0;
-      if (((p.ldr & 7) == 0) && ((reinterpret_cast<uintptr_t>(p.R) & 15) == 0) && col0 + 32 <= p.N) {
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const uint4 rv = __ldg(reinterpret_cast<const uint4*>(r) + j4);
-          const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 rf = __bfloat1622float2(r2[j]);
-            f[j4 * 8 + 2 * j] += rf.x;
-            f[j4 * 8 + 2 * j + 1] += rf.y;
-          }
-        }
-      } else {
-        for (int j = 0; j < 32; ++j)
-          if (col0 + j < p.N) f[j] += __bfloat162float(r[j]);
-      }
-    }
+    epilogue_values(p, row0 + lane, col0, v, f);
     const uint32_t mine = stage + lane * 64;
     const int sw = (lane >> 1) & 3;
 #pragma unroll

@@ -11,7 +11,6 @@ import pytest
 
 import habu_b200 as hb
 import oracle
-from oracle import decoder
 from util import SEED, bf16_close, bf16_normal, max_abs, max_rel
 
 pytestmark = pytest.mark.gpu
