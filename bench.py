@@ -64,6 +64,8 @@ class ClockSampler:
         self.bus_id, self.nvml, self.samples, self.stop_flag = bus_id, None, [], False
 
     def _start_nvml(self) -> bool:
+        if os.environ.get("HB_BENCH_CLOCK_SOURCE", "nvml") != "nvml":      # "nvidia-smi": the 100 ms sampler
+            return False
         try:
             import pynvml
             pynvml.nvmlInit()
