@@ -896,8 +896,11 @@ def main():
     pinned.keep = []
     pinned.placement = None
 
-    def measure(name, steps, warmup, full):
-        """Times one workload.  full=False: device-resident leg and parity check only."""
+    def measure(name, steps, warmup, full, min_ms=0.0):
+        """Times one workload.  full=False: device-resident leg and parity check only.  min_ms: a
+        step that is much shorter than a millisecond is repeated until the timed region lasts at
+        least that long (at most 2000 steps), so that the two event records and the first launch
+        do not weigh on it; `steps` in the result says how many were timed."""
         ctx = hb.Context(local_rank)
         ctx.set_stream(stream.cuda_stream)
         wl = WORKLOADS[name]()
@@ -947,6 +950,9 @@ def main():
 
         for _ in range(warmup):
             wl.step(ctx)
+        if min_ms > 0:
+            probe_ms = timed(wl.step, 3) / 3          # the same on every rank: timed() returns the max over ranks
+            steps = max(steps, min(2000, int(np.ceil(min_ms / max(probe_ms, 1e-4)))))
         sampler = ClockSampler(local_rank, bus_id)
         if rank == 0:
             sampler.start()
@@ -1022,7 +1028,15 @@ def main():
     extras = {}
     names = [] if args.extras == "none" else [e for e in args.extras.split(",") if e and e != args.workload]
     for name in names:
-        r = measure(name, max(3, min(args.steps, 20)), 3, False)
+        # an extra that fails must not cost the line its main figure: its entry carries the error instead.
+        # Under several ranks a failure is re-raised: the others would wait for this rank in the next barrier.
+        try:
+            r = measure(name, max(3, min(args.steps, 20)), 3, False, min_ms=20.0)
+        except Exception as e:
+            if world > 1:
+                raise
+            extras[name] = {"error": f"{type(e).__name__}: {e}"[:400]}
+            continue
         extras[name] = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "scaling", "workload", "l2",
                                           "roofline", "gpu_launches", "parity", "node_times") if k in r}
     if rank == 0:
