@@ -108,3 +108,23 @@ def test_stream_k_plan_covers_the_work_within_its_scratch(m, n, k):
     shortest = units // r.grid
     assert shortest >= 1
     assert -(-k_groups // shortest) + 1 <= r.max_segments or r.max_segments == r.grid
+
+
+def test_output_staging_swizzle_is_the_64_byte_tma_pattern():
+    """The GEMM epilogue writes piece c (16 bytes) of row r of a 32 x 32 bf16 block at
+    r*64 + ((c ^ ((r >> 1) & 3)) << 4) and stores the block with a 64-byte-swizzled tensor map.
+    That must be the hardware's pattern (address bits 4-5 xor-ed with bits 7-8 of a 512-byte
+    aligned buffer), fill the 2 KB buffer exactly once, and let the eight lanes of a quarter
+    warp hit eight different 16-byte bank groups."""
+    seen = set()
+    for r in range(32):
+        for c in range(4):
+            off = r * 64 + ((c ^ ((r >> 1) & 3)) << 4)
+            linear = r * 64 + c * 16                      # where the piece sits in the unswizzled block
+            assert off == linear ^ (((linear >> 7) & 3) << 4)
+            seen.add(off)
+    assert seen == set(range(0, 2048, 16))
+    for c in range(4):
+        for r0 in range(0, 32, 8):
+            groups = {((r * 64 + ((c ^ ((r >> 1) & 3)) << 4)) % 128) // 16 for r in range(r0, r0 + 8)}
+            assert len(groups) == 8
